@@ -82,7 +82,8 @@ def main(argv=None) -> int:
             return 2
         with open(args.random_config) as f:
             cj = json.load(f)
-        arch = tff.get_architecture(cj["architectures"][0])
+        from tffinfer_b200.config import architecture_name
+        arch = tff.get_architecture(architecture_name(cj))
         cfg = arch.read_config(cj)
         tff.write_random_model(args.save_model, cfg, seed=args.random_seed, store_dtype=args.store_dtype)
         print(f"wrote {args.save_model} (seed {args.random_seed}, {args.store_dtype})")

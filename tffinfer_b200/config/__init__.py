@@ -1,3 +1,4 @@
 from .model_config import (ModelConfig, Qwen3Config, ConfigError, read_config_json, write_config_json,
-                           FULL_ATTENTION, SLIDING_ATTENTION)
+                           FULL_ATTENTION, SLIDING_ATTENTION, architecture_name)
+from .tipezen_config import TipezenConfig, TipezenLayer, RotaryConfig
 from .engine_config import EngineConfig

@@ -231,3 +231,16 @@ def write_config_json(model_dir: str, cfg: ModelConfig) -> None:
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(cfg.to_json_dict(), f, indent=2)
         f.write("\n")
+
+
+def architecture_name(d: Dict[str, Any]) -> str:
+    """The name a config.json gives its architecture: ``architectures[0]`` (a list of names), or the
+    single name under ``architecture``."""
+    archs = d.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = d.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
+                      "(or 'architecture' a name)")

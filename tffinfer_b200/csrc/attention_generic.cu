@@ -6,11 +6,15 @@
 // For the token at position p of request b and query head h (kv head h / (nq/nkv),
 // src/kernel/cuda/paged_flash_attention.cu:891-892):
 //   s[n] = (q . k[n]) * scale for lo <= n <= p, lo = window ? max(0, p-window+1) : 0
+//   s[n] = softcap * tanh(s[n] / softcap)                      when softcap > 0
 //   out  = sum_n softmax(s)[n] * v[n]
 // with the running-maximum ("online") softmax of the reference
 // (paged_flash_attention.cu:696-792) in float32, over key blocks of 32 aligned to
 // absolute positions.  The block boundaries depend on p and the window only, so a
 // token's result does not depend on how the batch was cut or what else is in it.
+// With ``sink`` the softmax has one more term in its denominator, a key of score 0 that has no value:
+// weights exp(s[n]) / (1 + sum exp(s)).  With ``gate`` (float32 [tokens, nq]) the head's output is multiplied by
+// gate[t, h].  Keys have d elements and values dv; both lie in cache slots of dc >= max(d, dv) elements.
 #include "common.cuh"
 
 namespace {
@@ -23,8 +27,8 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
                          const int* __restrict__ positions, const int* __restrict__ tok_req,
                          const int* __restrict__ block_table, int table_width,
                          const T* __restrict__ cache, KvLayout L, int layer,
-                         T* __restrict__ out, int num_tokens, int nq, int nkv, int d,
-                         float scale, int window) {
+                         T* __restrict__ out, int num_tokens, int nq, int nkv, int d, int dv,
+                         float scale, int window, float softcap, int sink, const float* __restrict__ gate) {
     extern __shared__ float smem[];            // WARPS * d floats: the warp's query row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -40,11 +44,14 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
     __syncwarp();
 
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int nd = (d + 31) / 32;              // output dims per lane (<= 16 for d <= 512)
+    const int nd = (dv + 31) / 32;             // output dims per lane (<= 16 for dv <= 512)
+    const int dc = L.head_dim;                 // elements of a cache slot
     float o[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    // the sink is a key of score 0 ahead of all others: it starts the running maximum and the sum
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
     for (int k0 = (lo / 32) * 32; k0 <= p; k0 += 32) {
         const int n = k0 + lane;
@@ -54,11 +61,12 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
         if (valid) {
             const int page = table[n / L.page_size];
             const T* kbase = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
-                             (size_t)kvh * L.head_stride + (size_t)(n % L.page_size) * d;
+                             (size_t)kvh * L.head_stride + (size_t)(n % L.page_size) * dc;
             vbase = kbase + L.kv_stride;
             float acc = 0.f;
             for (int i = 0; i < d; ++i) acc = fmaf(q[i], to_f32<T>(kbase[i]), acc);
             s = acc * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
         }
         const float bm = warp_max(s);          // at least lane with n == max(k0, lo) .. is valid
         const float m_new = fmaxf(m, bm);
@@ -76,44 +84,57 @@ attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
             for (int j = 0; j < 16; ++j) {
                 if (j < nd) {
                     const int i = j * 32 + lane;
-                    if (i < d) o[j] = fmaf(pk, to_f32<T>(v[i]), o[j]);
+                    if (i < dv) o[j] = fmaf(pk, to_f32<T>(v[i]), o[j]);
                 }
             }
         }
         m = m_new;
     }
-    const float inv = 1.f / l;
-    T* orow = out + (size_t)t * nq * d + (size_t)h * d;
+    const float inv = (gate ? gate[(size_t)t * nq + h] : 1.f) / l;
+    T* orow = out + (size_t)t * nq * dv + (size_t)h * dv;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         if (j < nd) {
             const int i = j * 32 + lane;
-            if (i < d) orow[i] = from_f32<T>(o[j] * inv);
+            if (i < dv) orow[i] = from_f32<T>(o[j] * inv);
         }
     }
 }
 
 }  // namespace
 
-TFF_API int tff_attention_generic(
+// The general entry: keys of d and values of dv elements in cache slots of dc, score cap, sink, head gates.
+TFF_API int tff_attention_generic_ext(
     const void* qkv, int is_bf16, int row_stride,
     const int* positions, const int* tok_req, const int* block_table, int table_width,
     const void* cache, int cache_layers, int layer, int page_size,
-    void* out, int num_tokens, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    void* out, int num_tokens, int nq, int nkv, int d, int dv, int dc, float scale, int window,
+    float softcap, int sink, const float* gate, cudaStream_t stream) {
     if (num_tokens <= 0) return TFF_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page_size <= 0) return TFF_ERR_BAD_ARGUMENT;
-    if (d > 512) return TFF_ERR_UNSUPPORTED;
-    const KvLayout L = make_kv_layout(cache_layers, nkv, page_size, d);
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || dv <= 0 || dc < d || dc < dv || page_size <= 0 || softcap < 0.f)
+        return TFF_ERR_BAD_ARGUMENT;
+    if (d > 512 || dv > 512) return TFF_ERR_UNSUPPORTED;
+    const KvLayout L = make_kv_layout(cache_layers, nkv, page_size, dc);
     const long long items = (long long)num_tokens * nq;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const size_t smem = (size_t)WARPS * d * sizeof(float);
     if (is_bf16)
         attention_generic_kernel<bf16><<<blocks, WARPS * 32, smem, stream>>>(
             (const bf16*)qkv, row_stride, positions, tok_req, block_table, table_width,
-            (const bf16*)cache, L, layer, (bf16*)out, num_tokens, nq, nkv, d, scale, window);
+            (const bf16*)cache, L, layer, (bf16*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, gate);
     else
         attention_generic_kernel<float><<<blocks, WARPS * 32, smem, stream>>>(
             (const float*)qkv, row_stride, positions, tok_req, block_table, table_width,
-            (const float*)cache, L, layer, (float*)out, num_tokens, nq, nkv, d, scale, window);
+            (const float*)cache, L, layer, (float*)out, num_tokens, nq, nkv, d, dv, scale, window, softcap, sink, gate);
     return tff_launch_status();
+}
+
+TFF_API int tff_attention_generic(
+    const void* qkv, int is_bf16, int row_stride,
+    const int* positions, const int* tok_req, const int* block_table, int table_width,
+    const void* cache, int cache_layers, int layer, int page_size,
+    void* out, int num_tokens, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    return tff_attention_generic_ext(qkv, is_bf16, row_stride, positions, tok_req, block_table, table_width, cache,
+                                     cache_layers, layer, page_size, out, num_tokens, nq, nkv, d, d, d, scale, window,
+                                     0.f, 0, nullptr, stream);
 }

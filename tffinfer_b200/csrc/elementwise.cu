@@ -139,8 +139,14 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // columns, gate feature i at column (i / b) * 2b + i % b and its up feature b columns further.
 // ``clear`` != 0: the input is set to zero once it has been read (it is an accumulator buffer the
 // next split product adds into).
+// ``act`` = 0: silu as above; 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+
 template <typename TIN, typename T>
-__global__ void swiglu_kernel(TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter, int block, int clear) {
+__global__ void swiglu_kernel(TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter, int block, int clear, int act) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -151,23 +157,38 @@ __global__ void swiglu_kernel(TIN* __restrict__ gu, T* __restrict__ out, long lo
         const int uc = block > 0 ? gc + block : inter + i;
         const float g = to_f32<TIN>(gu[t * 2 * inter + gc]);
         const float u = to_f32<TIN>(gu[t * 2 * inter + uc]);
-        out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+        out[idx] = from_f32<T>(gate_activation(g, act) * u);
         if (clear) { gu[t * 2 * inter + gc] = from_f32<TIN>(0.f); gu[t * 2 * inter + uc] = from_f32<TIN>(0.f); }
     }
 }
 
 // dtype codes: 0 = float32, 1 = bfloat16; the input may be float32 with a bfloat16 output.
+static int gated_act_launch(void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block, int clear, int act,
+                            cudaStream_t stream);
+
 TFF_API int tff_swiglu(void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block, int clear,
                        cudaStream_t stream) {
+    return gated_act_launch(gu, in_dt, out, out_dt, rows, inter, block, clear, 0, stream);
+}
+
+// The same with the gate's activation chosen: act 0 = silu, 1 = gelu (tanh form).
+TFF_API int tff_gated_act(void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block, int clear, int act,
+                          cudaStream_t stream) {
+    if (act != 0 && act != 1) return TFF_ERR_BAD_ARGUMENT;
+    return gated_act_launch(gu, in_dt, out, out_dt, rows, inter, block, clear, act, stream);
+}
+
+static int gated_act_launch(void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block, int clear, int act,
+                            cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (inter <= 0 || block < 0 || (block > 0 && inter % block != 0)) return TFF_ERR_BAD_ARGUMENT;
     const long long total = (long long)rows * inter;
     const int nt = 256;
     const long long most = sm_count() * 16;
     const int blocks = (int)((total + nt - 1) / nt < most ? (total + nt - 1) / nt : most);
-    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (bf16*)gu, (bf16*)out, total, inter, block, clear);
-    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (float*)gu, (bf16*)out, total, inter, block, clear);
-    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (float*)gu, (float*)out, total, inter, block, clear);
+    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (bf16*)gu, (bf16*)out, total, inter, block, clear, act);
+    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (float*)gu, (bf16*)out, total, inter, block, clear, act);
+    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (float*)gu, (float*)out, total, inter, block, clear, act);
     return TFF_ERR_BAD_ARGUMENT;
 }
 

@@ -57,11 +57,8 @@ class ModelRunner:
         self.act_dtype = _TORCH_DTYPES[self.ecfg.dtype]
         if model_dir is not None:
             cj = read_config_json(model_dir)
-            archs = cj.get("architectures")
-            if not isinstance(archs, list) or not archs:
-                from ..config import ConfigError
-                raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
-            arch = get_architecture(archs[0])
+            from ..config import architecture_name
+            arch = get_architecture(architecture_name(cj))
             self.config = arch.read_config(cj)
         else:
             if config is None or tensors is None:

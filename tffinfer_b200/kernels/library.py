@@ -150,8 +150,17 @@ class CudaKernels:
         raise KernelError("the cache is neither contiguous nor a view of layer-major storage")
 
     # -------------------------------------------------------------- kernels
-    def embed(self, token_ids, table, out, scale: float = 1.0) -> None:
+    def embed(self, token_ids, table, out, scale: float = 1.0, copies: int = 0) -> None:
+        """out[t] = table[token_ids[t]] * scale; with ``copies`` = S > 0, out is [T, S, H] and every copy gets it."""
         self._need_cuda(token_ids, table, out)
+        if copies > 0:
+            T, S, H = out.shape
+            assert S == copies and token_ids.dtype == torch.int32 and out.dtype == torch.float32 and table.shape[1] == H
+            self._check(self.lib.tff_embed_streams(_ptr(token_ids), _ptr(table), _c_int(_dt(table)), _ptr(out), _c_int(T),
+                                                   _c_int(H), _c_int(table.shape[0]), _c_float(scale), _c_int(S),
+                                                   self._stream()), "embed_streams")
+            self.launches += 1
+            return
         T, H = out.shape
         assert token_ids.dtype == torch.int32 and out.dtype == torch.float32 and table.shape[1] == H
         self._check(self.lib.tff_embed(_ptr(token_ids), _ptr(table), _c_int(_dt(table)), _ptr(out),
@@ -388,12 +397,27 @@ class CudaKernels:
     def _foldable_weight(self, w) -> bool:
         return w.dtype == torch.bfloat16 and w.is_contiguous() and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0
 
-    def gated_mlp(self, h, w_gate_up, w_down, residual, inter: int) -> None:
-        """residual += down(silu(gate(h)) * up(h)); ``h`` the activation rows or a DeferredNorm of them.
+    ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}
+
+    def gated_mlp(self, h, w_gate_up, w_down, residual, inter: int, activation: str = "silu", out=None) -> None:
+        """residual += down(act(gate(h)) * up(h)); ``h`` the activation rows or a DeferredNorm of them.  With
+        ``residual`` None the result goes to ``out`` (float32 [T, hidden]) instead.  ``activation``: "silu" or
+        "gelu_tanh"; the kernels with the activation in a product's epilogue know silu only, another activation
+        runs the product and the activation kernel.
         A decode step of at most FOLD_MAX_M tokens in bfloat16 whose norm has been deferred runs two kernels:
         norm, gate/up product and SwiGLU as one (clusters of CTAs share a tile's K range), then the down
         product.  Everything else runs the products and kernels one by one."""
         T = h.shape[0]
+        if residual is None or activation != "silu":
+            if isinstance(h, DeferredNorm):
+                h = h.materialize()
+            act = torch.empty((T, inter), dtype=h.dtype, device=h.device)
+            self.gemm_gated_act(h, w_gate_up, act, activation)
+            if residual is None:
+                self.gemm(act, w_down, out)
+            else:
+                self.gemm(act, w_down, residual, residual=residual)
+            return
         if isinstance(h, DeferredNorm):
             if (self.gate_up_block(inter) == 64 and self._foldable_weight(w_gate_up)
                     and residual.is_cuda and residual.dtype == torch.float32):
@@ -432,6 +456,158 @@ class CudaKernels:
                                         _c_int(T), _c_int(I), _c_int(block), _c_int(clear), self._stream()), "swiglu")
         if clear:
             self._acc_zero[gate_up.data_ptr()] = True
+        self.launches += 1
+
+    def gated_act(self, gate_up, out, block: int = 0, activation: str = "silu") -> None:
+        """out[t, i] = act(gate[t, i]) * up[t, i], the layouts of ``swiglu``; act "silu" or "gelu_tanh"."""
+        self._need_cuda(gate_up, out)
+        T, I = out.shape
+        assert gate_up.shape == (T, 2 * I) and gate_up.dtype in (torch.float32, out.dtype)
+        clear = 1 if gate_up.data_ptr() in self._acc_zero else 0
+        self._check(self.lib.tff_gated_act(_ptr(gate_up), _c_int(_dt(gate_up)), _ptr(out), _c_int(_dt(out)), _c_int(T),
+                                           _c_int(I), _c_int(block), _c_int(clear),
+                                           _c_int(self.ACTIVATION_CODES[activation]), self._stream()), "gated_act")
+        if clear:
+            self._acc_zero[gate_up.data_ptr()] = True
+        self.launches += 1
+
+    def gemm_gated_act(self, a, w_gate_up, out, activation: str) -> None:
+        """out[T, I] = act(a @ Wg^T) * (a @ Wu^T), w_gate_up being merge_gate_up(Wg, Wu)."""
+        if activation == "silu":
+            return self.gemm_swiglu(a, w_gate_up, out)
+        T, I = out.shape
+        K = a.shape[1]
+        tc = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0
+              and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
+        if tc and T <= self.SWAP_MAX_M:
+            gu = self.projection_buffer(T, 2 * I, out.device, out.dtype)
+        else:
+            gu = torch.empty((T, 2 * I), dtype=out.dtype, device=out.device)
+        self.gemm(a, w_gate_up, gu)
+        self.gated_act(gu, out, self.gate_up_block(I), activation)
+
+    # ------------------------------------------------------- residual of several streams
+    def stream_step(self, x, y=None, scale=None, mix=None, out=None, read=None, norm_weight=None, eps: float = 0.0,
+                    h=None, row_index=None, total=None) -> None:
+        """x float32 [T, S, W], the residual's streams.  With ``y`` (float32 [T, W]): x_t <- sum_s mix[s, t] x_s +
+        out[t] * (scale * y) in place (mix [S, S], out [S], scale [W]; None = identity, ones, ones).  With ``h``
+        ([rows, W], activation type): h = rmsnorm(sum_s read[s] x_s) with ``norm_weight`` and ``eps`` (read None = ones).
+        With ``total`` (float32 [rows, W]): the combined row itself.  ``row_index`` (int32 [rows]) limits all of it to
+        those rows of x; h and total are then indexed by the place in ``row_index``."""
+        self._need_cuda(x, y, scale, mix, out, read, norm_weight, h, row_index, total)
+        T, S, W = x.shape
+        assert x.dtype == torch.float32
+        for t in (y, scale, mix, out, read, norm_weight, total):
+            assert t is None or t.dtype == torch.float32
+        assert y is None or tuple(y.shape) == (T, W)
+        assert mix is None or mix.numel() == S * S
+        assert out is None or out.numel() == S
+        assert read is None or read.numel() == S
+        assert scale is None or scale.numel() == W
+        rows = T if row_index is None else row_index.numel()
+        if row_index is not None:
+            assert row_index.dtype == torch.int32
+        if h is not None:
+            assert tuple(h.shape) == (rows, W)
+        if total is not None:
+            assert tuple(total.shape) == (rows, W)
+        self._check(self.lib.tff_stream_step(_ptr(x), _c_int(S), _c_int(W), _ptr(y), _ptr(scale), _ptr(mix), _ptr(out),
+                                             _ptr(read), _ptr(norm_weight), _c_float(eps), _ptr(row_index), _ptr(h),
+                                             _c_int(_dt(h)) if h is not None else _c_int(0), _ptr(total), _c_int(rows),
+                                             self._stream()), "stream_step")
+        self.launches += 1
+
+    # ------------------------------------------------------- mixers with a rotation computed on the fly
+    def qkv_finish(self, proj, q_out, k_out, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
+                   k_scale: float = 1.0, v_mode: int = 0, v_share=None, lam=None, gate_off: int = -1, gate_out=None) -> None:
+        """proj [T, ld] = [q (nq*d) | k (nkv*d) | v (nkv*dv) | ...] -> rotated q in ``q_out`` [T, nq*d]; rotated k
+        (times ``k_scale``) and v into the tokens' cache slots or, with no cache, k into ``k_out`` (float32);
+        ``freq`` = (frequencies, rot_dim, magnitude, interleaved) or None; value mixing and head gates as
+        csrc/qkv_finish.cu describes them."""
+        self._need_cuda(proj, q_out, k_out, block_table, v_share, lam, gate_out)
+        T, ld = proj.shape
+        f, rot, mag, inter = freq if freq is not None else (None, 0, 1.0, False)
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
+        dc = kv_cache.shape[-1] if kv_cache is not None else 0
+        if kv_cache is not None:
+            assert tuple(kv_cache.shape[2:5]) == (2, nkv, page_size)
+        self._check(self.lib.tff_qkv_finish(
+            _ptr(proj), _c_int(_dt(proj)), _c_int(ld), _ptr(q_out), _c_int(_dt(q_out)), _ptr(k_out),
+            _ptr(f), _c_int(rot), _c_float(mag), _c_int(1 if inter else 0), _c_float(k_scale),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
+            _c_int(block_table.shape[1] if block_table is not None else 0),
+            c_ptr, _c_int(_dt(kv_cache)) if kv_cache is not None else _c_int(0), _c_int(c_layers), _c_int(c_layer),
+            _c_int(page_size), _c_int(dc), _c_int(v_mode), _ptr(v_share), _ptr(lam), _c_int(gate_off), _ptr(gate_out),
+            _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), self._stream()), "qkv_finish")
+        self.launches += 1
+
+    def attend_gated(self, h, w_in, freq, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv,
+                     scale, window, softcap, sink, v_mode, v_share, lam, gate_off, write_cache) -> None:
+        """The whole of a gated, capped, sink attention between its input rows and its output projection: one product
+        for q, k, v and the head gates (``w_in`` rows [q | k | v | gates | padding]); rotation, value mixing, cache
+        write and sigmoid of the gates; attention over the paged cache with the cap, the window, the sink and the
+        gates -> out [T, nq*dv]."""
+        if not write_cache:
+            raise KernelError("attend_gated writes the keys and values it attends to; a borrowed cache is not supported")
+        T = h.shape[0]
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
+        proj = self.projection_buffer(T, w_in.shape[0], h.device, h.dtype)
+        self.gemm(h, w_in, proj)
+        q = torch.empty((T, nq * d), dtype=out.dtype, device=out.device)
+        gates = torch.empty((T, nq), dtype=torch.float32, device=out.device) if gate_off >= 0 else None
+        self.qkv_finish(proj, q, None, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
+                        1.0, v_mode, v_share, lam, gate_off, gates)
+        self.attention_ext(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale, window,
+                           softcap, sink, gates)
+
+    def attention_ext(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale, window,
+                      softcap: float = 0.0, sink: bool = False, gates=None) -> None:
+        """q [T, nq*d] against the paged cache (slots of kv_cache.shape[-1] >= max(d, dv) elements) -> out [T, nq*dv],
+        with a cap on the scores, a sink in the softmax and a multiplier per (token, head)."""
+        self._need_cuda(q, block_table, out, gates)
+        T = q.shape[0]
+        dc = kv_cache.shape[-1]
+        assert kv_cache.dtype == q.dtype == out.dtype
+        assert tuple(q.shape) == (T, nq * d) and tuple(out.shape) == (T, nq * dv)
+        assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, dc) and dc >= max(d, dv)
+        assert gates is None or (gates.dtype == torch.float32 and tuple(gates.shape) == (T, nq))
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
+        self._check(self.lib.tff_attention_generic_ext(
+            _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
+            c_ptr, _c_int(c_layers), _c_int(c_layer), _c_int(page_size),
+            _ptr(out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_int(dc), _c_float(scale),
+            _c_int(window), _c_float(softcap), _c_int(1 if sink else 0), _ptr(gates), self._stream()),
+            "attention_generic_ext")
+        self.launches += 1
+
+    def retain(self, h, w_in, freq, batch, state, decay, out, H, d, dv, k_scale: float, eps: float) -> None:
+        """The whole of a retention mixer between its input rows and its output projection: one product for q, k, v
+        and the gate (``w_in`` rows [q | k | v | gate | padding]) into float32; rotation of q and k (k times
+        ``k_scale``), float32; the recurrence over ``state`` [slots, H, d, dv] with ``decay`` [H], the per-head RMS
+        norm and the silu gate -> out [T, H*dv].  Steps in which every request brings one token run token by token,
+        the others chunk by chunk."""
+        T = h.shape[0]
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
+        self._need_cuda(state, decay, out)
+        assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (H, d, dv) and decay.numel() == H
+        proj = self.projection_buffer(T, w_in.shape[0], h.device, h.dtype)
+        self.gemm(h, w_in, proj)
+        q = torch.empty((T, H * d), dtype=torch.float32, device=h.device)
+        k = torch.empty((T, H * d), dtype=torch.float32, device=h.device)
+        self.qkv_finish(proj, q, k, freq, batch, None, None, 0, 0, H, H, d, dv, k_scale)
+        ld, v_off, g_off = proj.shape[1], 2 * H * d, 2 * H * d + H * dv
+        chunked = 0 if batch.max_q_len == 1 else 1
+        args = lambda ch: (_ptr(q), _ptr(k), _ptr(proj), _c_int(ld), _c_int(v_off), _c_int(g_off), _ptr(state),
+                           _c_int(state.shape[0]), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(batch.slots),
+                           _ptr(decay), _ptr(out), _c_int(_dt(out)), _c_int(batch.num_requests), _c_int(H), _c_int(d),
+                           _c_int(dv), _c_float(eps), _c_int(ch), self._stream())
+        status = self.lib.tff_retention(*args(chunked))
+        if status == -2 and chunked:
+            status = self.lib.tff_retention(*args(0))      # heads too large for the chunked kernel's shared memory
+        self._check(status, "retention")
         self.launches += 1
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:

@@ -1,2 +1,3 @@
 """Architectures.  Importing this package registers them."""
 from . import qwen3  # noqa: F401
+from . import tipezen  # noqa: F401  (registration)

@@ -82,3 +82,104 @@ class GQAttention(Mixer):
                    self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window, ctx.write_cache)
         ops.gemm(attn, self.w_o, residual, residual=residual)
         return residual
+
+
+@register_part("mixer", "gated_sink_attention")
+class GatedSinkAttention(Mixer):
+    """Grouped-query attention over the paged cache with what several newer designs add to it, each a parameter:
+
+    * keys/queries of ``head_dim`` and values of ``v_head_dim`` elements;
+    * a rotation of part of the head given by the layer's position encoding (``frequencies()``);
+    * scores ``(q . k) * softmax_scale``, then ``softcap * tanh(score / softcap)`` when ``softcap`` > 0;
+    * a sliding ``window`` (a query at position p sees keys p-window+1 .. p; 0 = all earlier keys);
+    * ``sink``: one more term in the softmax's denominator, a key of score 0 without a value;
+    * ``value_mix``: "source" leaves this layer's values of the step's tokens in ``ctx.shared[value_key]``;
+      "mix" replaces its own by ``(1 - lambda) v + lambda v_source`` with a learned scalar lambda before they are
+      cached; "none" does neither;
+    * ``head_gate``: every head's output is multiplied by ``sigmoid(W_g h)`` of that head, W_g [heads, hidden], read
+      from the mixer's input like the projections.
+
+    The q, k, v and gate projections are one product.  ``names`` gives the tensor names of "q", "k", "v", "o",
+    "gate" and "lambda" relative to the prefix."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int = 0,
+                 softmax_scale: Optional[float] = None, softcap: float = 0.0, window: int = 0, sink: bool = False,
+                 value_mix: str = "none", value_key: str = "values", head_gate: bool = False,
+                 lambda_tensor: bool = False, names: Optional[Dict[str, str]] = None, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.v_head_dim = int(v_head_dim) if v_head_dim else int(head_dim)
+        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.softcap, self.window, self.sink = float(softcap), int(window), bool(sink)
+        if value_mix not in ("none", "source", "mix"):
+            raise ValueError(f"value_mix must be 'none', 'source' or 'mix', got '{value_mix}'")
+        self.value_mix, self.value_key, self.head_gate = value_mix, value_key, bool(head_gate)
+        self.lambda_tensor = bool(lambda_tensor) or value_mix == "mix"   # a "source" layer may carry an unused one
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                      "gate": "gate_proj.weight", "lambda": "value_lambda"}
+        self.names.update(names or {})
+        self.q_width = self.num_heads * self.head_dim
+        self.k_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_kv_heads * self.v_head_dim
+        self.cache_dim = max(self.head_dim, self.v_head_dim)     # a cache slot holds a key or a value
+        self.w_in = self.w_o = self.lam = None
+
+    def cache_need(self):
+        return KVNeed(self.num_kv_heads, self.cache_dim, self.window)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n = self.names
+        s = {n["q"]: WeightSpec((self.q_width, self.hidden_size), MATRIX),
+             n["k"]: WeightSpec((self.k_width, self.hidden_size), MATRIX),
+             n["v"]: WeightSpec((self.v_width, self.hidden_size), MATRIX),
+             n["o"]: WeightSpec((self.hidden_size, self.num_heads * self.v_head_dim), MATRIX)}
+        if self.head_gate:
+            s[n["gate"]] = WeightSpec((self.num_heads, self.hidden_size), MATRIX)
+        if self.lambda_tensor:
+            s[n["lambda"]] = WeightSpec((), VECTOR, init="normal", init_scale=0.3)
+        return s
+
+    def load(self, tensors, ops, act_dtype) -> None:
+        n = self.names
+        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        if self.head_gate:
+            rows.append(tensors[n["gate"]])
+        dt = rows[0].dtype if all(r.dtype == rows[0].dtype for r in rows) else torch.float32
+        w = torch.cat([r.to(dt) for r in rows], dim=0)
+        pad = (-w.shape[0]) % 8               # the product's output rows are stored 16 bytes at a time
+        if pad:
+            w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=dt, device=w.device)], dim=0)
+        self.w_in = w.contiguous()
+        self.gate_off = self.q_width + self.k_width + self.v_width
+        self.w_o = tensors[n["o"]]
+        if self.lambda_tensor:
+            self.lam = tensors[n["lambda"]].reshape(1).contiguous()
+
+    def forward(self, h, ctx: LayerContext, residual):
+        ops, batch = ctx.ops, ctx.batch
+        T = h.shape[0]
+        freq = ctx.position.frequencies() if ctx.position is not None else None
+        share = None
+        if self.value_mix == "source":
+            share = torch.empty((T, self.v_width), dtype=torch.float32, device=h.device)
+            ctx.shared[self.value_key] = share
+        elif self.value_mix == "mix":
+            share = ctx.shared.get(self.value_key)
+            if share is None or tuple(share.shape) != (T, self.v_width):
+                raise ValueError(f"value_mix='mix' needs the values of an earlier layer of this step under "
+                                 f"'{self.value_key}' with {self.v_width} elements a token")
+        attn = torch.empty((T, self.num_heads * self.v_head_dim), dtype=h.dtype, device=h.device)
+        ops.attend_gated(h, self.w_in, freq, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, attn,
+                         self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.scale, self.window,
+                         self.softcap, self.sink, {"none": 0, "source": 1, "mix": 2}[self.value_mix], share,
+                         self.lam if self.value_mix == "mix" else None,
+                         self.gate_off if self.head_gate else -1, ctx.write_cache)
+        if residual is None:
+            out = torch.empty((T, self.hidden_size), dtype=torch.float32, device=h.device)
+            ops.gemm(attn, self.w_o, out)
+            return out
+        ops.gemm(attn, self.w_o, residual, residual=residual)
+        return residual

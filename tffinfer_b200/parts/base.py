@@ -56,6 +56,9 @@ class LayerContext:
     write_cache  False when this run reads another run's cache
     state        tensor [slots, *StateNeed.shape] of this run, or None
     position     the layer's position-encoding part, or None
+    shared       a dict that lives for one step, the same object for every layer run: a mixer may leave
+                 tensors of this step's tokens there for the layers behind it (values that later layers mix
+                 into their own, for instance)
     """
     batch: Any
     ops: Any
@@ -66,6 +69,7 @@ class LayerContext:
     write_cache: bool = True
     state: Optional[torch.Tensor] = None
     position: Any = None
+    shared: Optional[Dict[str, Any]] = None    # lives for one step: what a layer leaves for later layers of the step
 
 
 class Part:
@@ -109,12 +113,18 @@ class PositionEncoding(Part):
         """(cos_sin table float32 [max_position, rot_dim/2, 2], rot_dim) or None."""
         return None
 
+    def frequencies(self):
+        """For rotations computed from the position on the fly: (frequencies float32 [rot_dim/2] on the device,
+        rot_dim, magnitude of cos and sin, interleaved pairs or halves), or None."""
+        return None
+
 
 class Mixer(Part):
     """Mixes information between the tokens of a request (attention here).
 
     cache_need() -> KVNeed | StateNeed | None
-    forward(h, ctx, residual) -> float32 [T, hidden]: residual + mixer(h)
+    forward(h, ctx, residual) -> float32 [T, hidden]: residual + mixer(h); with ``residual`` None, mixer(h)
+    alone in a tensor of its own (arrangements that do something else with it than add it to one stream).
     """
     def cache_need(self):
         return None
@@ -124,8 +134,22 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """forward(h, ctx, residual) -> float32 [T, hidden]: residual + f(h)."""
+    """forward(h, ctx, residual) -> float32 [T, hidden]: residual + f(h); with ``residual`` None, f(h) alone."""
     def forward(self, h: torch.Tensor, ctx: LayerContext, residual: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Connector(Part):
+    """How a sublayer reads its input from the residual and how its output joins it, where that is more than
+    ``norm(x)`` and ``x + y``: the residual is then a :class:`parts.streams.ResidualStreams`.
+
+    read(x, norm, ops, out_dtype) -> activation rows [T, hidden]
+    write(x, y) -> None (x is updated; the update may be deferred to the next read)
+    """
+    def read(self, x, norm, ops, out_dtype):
+        raise NotImplementedError
+
+    def write(self, x, y) -> None:
         raise NotImplementedError
 
 
@@ -136,16 +160,19 @@ class Block:
     family = "block"
     kind = ""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Optional[Norm] = None,
-                 ffn_norm: Optional[Norm] = None, extra_norms: Optional[Dict[str, Norm]] = None):
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Optional[Norm] = None,
+                 ffn_norm: Optional[Norm] = None, extra_norms: Optional[Dict[str, Norm]] = None,
+                 connectors: Optional[Dict[str, "Connector"]] = None):
         self.mixer = mixer
-        self.feed_forward = feed_forward
+        self.feed_forward = feed_forward          # None: the layer has no feed-forward (where the arrangement allows)
         self.mixer_norm = mixer_norm
         self.ffn_norm = ffn_norm
         self.extra_norms = dict(extra_norms or {})
+        self.connectors = dict(connectors or {})  # by a name of the arrangement's choosing
 
     def parts(self):
-        named = [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward] + list(self.extra_norms.values())
+        named = [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward] + list(self.extra_norms.values()) + \
+                list(self.connectors.values())
         return [p for p in named if p is not None]
 
     def forward(self, x: torch.Tensor, ctx: LayerContext, act_dtype: torch.dtype) -> torch.Tensor:

@@ -27,14 +27,17 @@ class LayerSpec:
     are wired around the residual stream; ``mixer_norm`` and ``ffn_norm`` are the norms the pre-norm
     arrangement uses, ``extra_norms`` any further norms another arrangement names (after the mixer, after the
     feed-forward, ...), by a name of the arrangement's choosing.  ``position`` names an entry of
-    ``ModelDescription.positions`` (or None)."""
+    ``ModelDescription.positions`` (or None).  ``feed_forward`` None is a layer of a mixer alone (for
+    arrangements that allow it); ``connectors`` are the parts that join sublayers to a residual of several
+    streams (registry family "connector"), by a name of the arrangement's choosing."""
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: Optional[PartSpec] = None
     ffn_norm: Optional[PartSpec] = None
     block: str = "pre_norm"
     position: Optional[str] = None
     extra_norms: Dict[str, PartSpec] = field(default_factory=dict)
+    connectors: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass
@@ -62,6 +65,9 @@ class ModelDescription:
     embed_scale: float = 1.0              # the embedding rows are multiplied by this (1: as they are)
     logit_scale: float = 1.0              # the logits are multiplied by this ...
     logit_softcap: float = 0.0            # ... and then, if > 0, squashed: softcap * tanh(logit / softcap)
+    streams: int = 0                      # 0: the residual is one tensor [T, hidden].  S >= 1: it is S copies of the
+                                          # embedding output (parts/streams.py), read and written through the layers'
+                                          # connectors; the final norm reads their sum
 
     def validate(self) -> "ModelDescription":
         for i, e in enumerate(self.schedule):

@@ -2,7 +2,9 @@
 ``silu(g) = g / (1 + exp(-g))`` as the reference computes it
 (src/kernel/cuda/unary.cu:10-27; built by ModelCreatorBase::build_ffn,
 src/core/model/base/ModelCreatorBase.cpp:51-94), followed by the residual add
-(src/core/model/qwen3/QWen3Creator.cpp:148-151)."""
+(src/core/model/qwen3/QWen3Creator.cpp:148-151).  ``activation`` chooses the gate's function: "silu", or
+"gelu_tanh", ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))``; ``names`` the tensor names of "gate", "up" and
+"down" relative to the prefix."""
 from __future__ import annotations
 
 from typing import Dict
@@ -17,26 +19,44 @@ from .base import FeedForward, WeightSpec, MATRIX
 class SwiGLU(FeedForward):
     takes_deferred_norm = True        # the input only feeds the gate/up product
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", names=None,
+                 prefix: str = ""):
         super().__init__(prefix)
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation must be one of {self.ACTIVATIONS}, got '{activation}'")
+        self.activation = activation
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
         self.w_gate_up = self.w_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
+        n = self.names
         return {
-            "gate_proj.weight": WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
-            "up_proj.weight": WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
-            "down_proj.weight": WeightSpec((self.hidden_size, self.intermediate_size), MATRIX),
+            n["gate"]: WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
+            n["up"]: WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
+            n["down"]: WeightSpec((self.hidden_size, self.intermediate_size), MATRIX),
         }
 
     def load(self, tensors, ops, act_dtype) -> None:
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
         # one projection instead of two; the kernel library chooses how gate and up rows are laid out
         self.w_gate_up = ops.merge_gate_up(g.to(dt), u.to(dt))
-        self.w_down = tensors["down_proj.weight"]
+        self.w_down = tensors[self.names["down"]]
 
     def forward(self, h, ctx, residual):
-        ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, residual, self.intermediate_size)
+        if residual is None:              # f(h) alone, for arrangements that do more with it than add it
+            out = torch.empty((h.shape[0], self.hidden_size), dtype=torch.float32, device=h.device)
+            ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, None, self.intermediate_size,
+                              activation=self.activation, out=out)
+            return out
+        if self.activation == "silu":
+            ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, residual, self.intermediate_size)
+        else:
+            ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, residual, self.intermediate_size,
+                              activation=self.activation)
         return residual

@@ -38,16 +38,20 @@ class Model:
         self.blocks: List[Block] = []
         for ls in desc.layers:
             block_cls = get_part("block", ls.block)
+            kw = {}
+            if ls.connectors:
+                kw["connectors"] = {name: build_part("connector", ps) for name, ps in ls.connectors.items()}
             self.blocks.append(block_cls(
                 mixer=build_part("mixer", ls.mixer),
-                feed_forward=build_part("feed_forward", ls.feed_forward),
+                feed_forward=build_part("feed_forward", ls.feed_forward) if ls.feed_forward is not None else None,
                 mixer_norm=build_part("norm", ls.mixer_norm) if ls.mixer_norm is not None else None,
                 ffn_norm=build_part("norm", ls.ffn_norm) if ls.ffn_norm is not None else None,
-                extra_norms={name: build_part("norm", ps) for name, ps in ls.extra_norms.items()}))
+                extra_norms={name: build_part("norm", ps) for name, ps in ls.extra_norms.items()}, **kw))
         self.layer_position = [self.positions[ls.position] if ls.position else None for ls in desc.layers]
         self.final_norm = build_part("norm", desc.final_norm)
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+        self.layer_hook = None      # optional callable(run index, float32 [T, hidden]): the residual after every layer run
 
     # ---------------------------------------------------------------- weights
     def all_parts(self) -> List[Part]:
@@ -97,10 +101,15 @@ class Model:
         logits [len(batch.logit_rows), vocab]."""
         d = self.desc
         T = batch.num_tokens
-        x = torch.empty((T, d.hidden_size), dtype=torch.float32, device=self.embed.device)
-        ops.embed(batch.token_ids, self.embed, x, d.embed_scale)
+        if d.streams > 0:
+            from .streams import ResidualStreams
+            x = ResidualStreams.from_embedding(batch.token_ids, self.embed, d.embed_scale, d.streams, ops)
+        else:
+            x = torch.empty((T, d.hidden_size), dtype=torch.float32, device=self.embed.device)
+            ops.embed(batch.token_ids, self.embed, x, d.embed_scale)
         for pos in self.positions.values():
             x = pos.embed(x, batch, ops)
+        shared: Dict[str, torch.Tensor] = {}
         for e, entry in enumerate(d.schedule):
             b = bindings[e]
             ctx = LayerContext(
@@ -110,13 +119,18 @@ class Model:
                 block_table=block_tables[b.group] if b.group is not None else None,
                 page_size=page_size, write_cache=b.write,
                 state=states[b.state_index] if b.state_index is not None else None,
-                position=self.layer_position[entry.layer])
+                position=self.layer_position[entry.layer], shared=shared)
             x = self.blocks[entry.layer].forward(x, ctx, act_dtype)
+            if self.layer_hook is not None:
+                self.layer_hook(e, x.total() if d.streams > 0 else x)
         R = batch.num_logit_rows
         if R == 0:
-            return torch.empty((0, d.vocab_size), dtype=torch.float32, device=x.device)
-        hn = self.final_norm.forward(x, ops, act_dtype, row_index=batch.logit_rows)
-        logits = torch.empty((R, d.vocab_size), dtype=torch.float32, device=x.device)
+            return torch.empty((0, d.vocab_size), dtype=torch.float32, device=self.embed.device)
+        if d.streams > 0:
+            hn = x.read(None, self.final_norm, ops, act_dtype, row_index=batch.logit_rows)
+        else:
+            hn = self.final_norm.forward(x, ops, act_dtype, row_index=batch.logit_rows)
+        logits = torch.empty((R, d.vocab_size), dtype=torch.float32, device=self.embed.device)
         ops.gemm(hn, self.lm_head, logits)
         if d.logit_scale != 1.0 or d.logit_softcap > 0.0:
             ops.logit_transform(logits, d.logit_scale, d.logit_softcap)

@@ -14,17 +14,18 @@ from .base import Norm, WeightSpec, VECTOR
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
-    def __init__(self, dim: int, eps: float, prefix: str = ""):
+    def __init__(self, dim: int, eps: float, name: str = "weight", prefix: str = ""):
         super().__init__(prefix)
         self.dim = int(dim)
         self.eps = float(eps)
+        self.name = name                  # the weight's tensor name relative to the prefix
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.dim,), VECTOR, init="one_plus_normal")}
+        return {self.name: WeightSpec((self.dim,), VECTOR, init="one_plus_normal")}
 
     def load(self, tensors, ops, act_dtype) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.name]
 
     def deferred(self, x, ops, out_dtype):
         """The norm of ``x`` as an object that the kernel library's products can fold in, or None when the

@@ -34,3 +34,56 @@ class RotaryPosition(PositionEncoding):
 class NoPosition(PositionEncoding):
     def __init__(self, prefix: str = ""):
         super().__init__(prefix)
+
+
+def scaled_frequencies(rot_dim: int, base: float, scaling=None):
+    """(frequencies as a list of rot_dim/2 floats, magnitude of cos and sin).  Plain: f_i = base^(-2i/rot_dim),
+    magnitude 1.  With ``scaling`` = (factor, original, fast, slow), the YaRN rule: the dimension at which a
+    position of ``original`` makes ``t`` turns is dim(t) = rot_dim ln(original / (2 pi t)) / (2 ln base);
+    between lo = max(floor(dim(fast)), 0) and hi = min(ceil(dim(slow)), rot_dim - 1) a ramp r_i =
+    clamp((i - lo) / max(hi - lo, 0.001), 0, 1) takes f_i over to f_i / factor (f_i (1 - r_i) + f_i / factor r_i),
+    and cos and sin are multiplied by 0.1 ln(factor) + 1.  Evaluated in double; the caller rounds once."""
+    import math
+    half = rot_dim // 2
+    f = [base ** (-2.0 * i / rot_dim) for i in range(half)]
+    if scaling is None:
+        return f, 1.0
+    factor, original, fast, slow = (float(v) for v in scaling)
+
+    def dim_of(turns: float) -> float:
+        return rot_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), rot_dim - 1)
+    out = []
+    for i, fi in enumerate(f):
+        r = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(fi / factor * r + fi * (1.0 - r))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+@register_part("position", "scaled_rotary")
+class ScaledRotary(PositionEncoding):
+    """A rotation of the first ``rotary_dim`` dimensions of a head whose angles are computed from the position
+    where they are applied (no table, so no longest position): pair i at position p turns by float32(p) *
+    float32(f_i).  ``pairing``: "interleaved" pairs dimension 2i with 2i+1, "halves" pairs i with i + rotary_dim/2.
+    ``scaling`` rescales the frequencies and the magnitude (scaled_frequencies above)."""
+    def __init__(self, rotary_dim: int, theta: float, pairing: str = "halves", scaling=None, prefix: str = ""):
+        super().__init__(prefix)
+        self.rotary_dim = int(rotary_dim)
+        self.theta = float(theta)
+        if pairing not in ("interleaved", "halves"):
+            raise ValueError(f"pairing must be 'interleaved' or 'halves', got '{pairing}'")
+        if self.rotary_dim <= 0 or self.rotary_dim % 2:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and positive")
+        self.interleaved = pairing == "interleaved"
+        self.scaling = tuple(scaling) if scaling is not None else None
+        self.freq = None
+        self.magnitude = 1.0
+
+    def prepare(self, ops, device, max_position: int) -> None:
+        f, self.magnitude = scaled_frequencies(self.rotary_dim, self.theta, self.scaling)
+        self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+
+    def frequencies(self):
+        return self.freq, self.rotary_dim, self.magnitude, self.interleaved
