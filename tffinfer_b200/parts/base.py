@@ -22,7 +22,7 @@ INT_TABLE = "int"      # integer tables: held in int32
 class WeightSpec:
     shape: Tuple[int, ...]
     role: str = MATRIX
-    init: str = "normal"          # random-weights mode: "normal" | "one_plus_normal" | "zeros"
+    init: str = "normal"          # random-weights mode: "normal" | "one_plus_normal" | "eye_plus_normal" | "zeros"
     init_scale: Optional[float] = None   # std; None = the model's init_std (normal) or 0.1 (one_plus_normal)
 
 

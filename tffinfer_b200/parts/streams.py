@@ -94,7 +94,7 @@ class HyperConnection(Connector):
         if self.learned:
             s[n["read"]] = WeightSpec((S,), VECTOR, init="one_plus_normal", init_scale=0.3)
             s[n["write"]] = WeightSpec((S,), VECTOR, init="one_plus_normal", init_scale=0.3)
-            s[n["mix"]] = WeightSpec((S, S), VECTOR, init="normal", init_scale=0.4)
+            s[n["mix"]] = WeightSpec((S, S), VECTOR, init="eye_plus_normal", init_scale=0.25)
         if self.layer_scale:
             s[n["scale"]] = WeightSpec((self.hidden_size,), VECTOR, init="one_plus_normal", init_scale=0.3)
         return s

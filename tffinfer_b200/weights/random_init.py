@@ -38,6 +38,9 @@ def random_tensor(seed: int, name: str, spec: WeightSpec, init_std: float, norm_
     elif spec.init == "one_plus_normal":
         s = norm_noise if spec.init_scale is None else spec.init_scale
         t = 1.0 + s * torch.randn(spec.shape, generator=g, dtype=torch.float32)
+    elif spec.init == "eye_plus_normal":      # a square matrix near the identity
+        s = norm_noise if spec.init_scale is None else spec.init_scale
+        t = torch.eye(spec.shape[0], dtype=torch.float32) + s * torch.randn(spec.shape, generator=g, dtype=torch.float32)
     else:
         s = init_std if spec.init_scale is None else spec.init_scale
         t = s * torch.randn(spec.shape, generator=g, dtype=torch.float32)
@@ -82,6 +85,12 @@ def random_tensors_on_device(cfg: ModelConfig, seed: int, device, store_dtype: s
         elif spec.init == "one_plus_normal":
             s = norm_noise if spec.init_scale is None else spec.init_scale
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            if s:
+                t += s * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+            out[name] = t.to(sd)
+        elif spec.init == "eye_plus_normal":
+            s = norm_noise if spec.init_scale is None else spec.init_scale
+            t = torch.eye(spec.shape[0], dtype=torch.float32, device=device)
             if s:
                 t += s * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
             out[name] = t.to(sd)
