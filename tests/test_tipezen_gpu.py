@@ -134,9 +134,14 @@ def fake_batch(lens, starts, dev, page, slots=None):
         k = -(-(s + n) // page)
         table.append(list(range(nxt, nxt + k)) + [-1] * (width - k))
         nxt += k
+    import numpy as np
+    order = sorted(range(len(lens)), key=lambda b: (lens[b], -(starts[b] + lens[b])))   # as the engine packs a step
     return SimpleNamespace(positions=t(pos), tok_req=t(req), q_start=t(qs), pos_start=t(starts),
                            slots=t(slots if slots is not None else list(range(len(lens)))), num_requests=len(lens),
-                           max_q_len=max(lens), num_tokens=len(pos), block_table=t(table), pages=nxt)
+                           max_q_len=max(lens), num_tokens=len(pos), block_table=t(table), pages=nxt,
+                           max_kv_len=max(s + n for n, s in zip(lens, starts)), req_order=t(order),
+                           h_sorted_q_lens=np.array([lens[b] for b in order]),
+                           h_sorted_kv_lens=np.array([starts[b] + lens[b] for b in order]), key_split_class=None)
 
 
 @pytest.fixture(scope="module")

@@ -65,6 +65,7 @@ struct AttnParams {
     const bf16* cache; KvLayout L; int layer;
     bf16* out; float* part_o; float* part_ml; int num_splits;
     int nq, nkv; float scale_log2; int window;
+    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
 };
 
 template <int D, bool KEYS_MODE>
@@ -201,7 +202,7 @@ attn_fwd_kernel(const AttnParams p) {
                 const int n = nbase + nt * 8 + (e & 1);
                 const bool up = e < 2;
                 const bool ok = up ? (v0 && n <= pr0 && n >= lo0) : (v1 && n <= pr1 && n >= lo1);
-                const float x = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                const float x = ok ? attn_score_log2(s[nt][e], p.scale_log2, p.scale_over_cap, p.cap_log2) : -INFINITY;
                 s[nt][e] = x;
                 if (up) bm0 = fmaxf(bm0, x); else bm1 = fmaxf(bm1, x);
             }
@@ -284,7 +285,9 @@ attn_fwd_kernel(const AttnParams p) {
             }
             const size_t grow = (size_t)(q0 + R / G) * p.nq + (kvh * G + R % G);
             if (p.num_splits == 1) {
-                p.out[grow * D + c] = __float2bfloat16_rn(acc / lsum);
+                if (p.sink) lsum += exp2f(-Ms);                    // the sink: a key of score 0
+                const float gt = p.gate ? p.gate[grow] : 1.f;
+                p.out[grow * D + c] = __float2bfloat16_rn(acc * gt / lsum);
             } else {
                 p.part_o[(grow * p.num_splits + split) * D + c] = acc;
                 if (c == 0) {
@@ -297,7 +300,11 @@ attn_fwd_kernel(const AttnParams p) {
         const size_t g0 = (size_t)(q0 + R0 / G) * p.nq + (kvh * G + R0 % G);
         const size_t g1 = (size_t)(q0 + R1 / G) * p.nq + (kvh * G + R1 % G);
         if (p.num_splits == 1) {
-            const float i0 = 1.f / l0, i1 = 1.f / l1;
+            if (p.sink) {                                          // the sink: a key of score 0
+                l0 += exp2f(m0 == -INFINITY ? 0.f : -m0);
+                l1 += exp2f(m1 == -INFINITY ? 0.f : -m1);
+            }
+            const float i0 = ((p.gate && v0) ? p.gate[g0] : 1.f) / l0, i1 = ((p.gate && v1) ? p.gate[g1] : 1.f) / l1;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
                 const int c = i * 8 + 2 * (lane & 3);
@@ -325,7 +332,7 @@ attn_fwd_kernel(const AttnParams p) {
 // once (two round trips to memory, not two per split)
 template <int D, int MAXS>
 __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            bf16* __restrict__ out, int num_splits, size_t row) {
+                                            bf16* __restrict__ out, int num_splits, size_t row, int sink, float gt) {
     float2 ml[MAXS];
 #pragma unroll
     for (int s = 0; s < MAXS; ++s)
@@ -340,6 +347,7 @@ __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, co
         f[s] = (s < num_splits && ml[s].y != 0.f) ? exp2f(ml[s].x - Ms) : 0.f;   // an empty split counts for nothing
         lsum += f[s] * ml[s].y;
     }
+    if (sink) lsum += exp2f(-Ms);                                           // the sink: a key of score 0
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float po[MAXS];
 #pragma unroll
@@ -348,14 +356,14 @@ __device__ __forceinline__ void combine_row(const float* __restrict__ part_o, co
         float acc = 0.f;
 #pragma unroll
         for (int s = 0; s < MAXS; ++s) acc += f[s] * po[s];
-        out[row * D + c] = __float2bfloat16_rn(acc / lsum);
+        out[row * D + c] = __float2bfloat16_rn(acc * gt / lsum);
     }
 }
 
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits, const int* __restrict__ q_start,
-                                    const int* __restrict__ req_ids, int nq) {
+                                    const int* __restrict__ req_ids, int nq, int sink, const float* __restrict__ gate) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     // the step's batch arrays are older than the kernel ahead: they are read before waiting for it
     const int b = req_ids ? req_ids[blockIdx.y] : (int)blockIdx.y;
@@ -365,9 +373,10 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     pdl_wait();
     if (t >= q_len) return;
     const size_t row = (size_t)(q0 + t) * nq + h;
-    if (num_splits <= 4) { combine_row<D, 4>(part_o, part_ml, out, num_splits, row); return; }
-    if (num_splits <= 8) { combine_row<D, 8>(part_o, part_ml, out, num_splits, row); return; }
-    if (num_splits <= 16) { combine_row<D, 16>(part_o, part_ml, out, num_splits, row); return; }
+    const float gt = gate ? gate[row] : 1.f;
+    if (num_splits <= 4) { combine_row<D, 4>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
+    if (num_splits <= 8) { combine_row<D, 8>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
+    if (num_splits <= 16) { combine_row<D, 16>(part_o, part_ml, out, num_splits, row, sink, gt); return; }
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
     const float Ms = M == -INFINITY ? 0.f : M;
@@ -380,7 +389,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
             acc += f * part_o[(row * num_splits + s) * D + c];
             lsum += f * l;
         }
-        out[row * D + c] = __float2bfloat16_rn(acc / lsum);
+        if (sink) lsum += exp2f(-Ms);
+        out[row * D + c] = __float2bfloat16_rn(acc * gt / lsum);
     }
 }
 
@@ -415,8 +425,9 @@ static int attention_bf16_impl(
     const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
-    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    int nq, int nkv, int d, float scale, int window, AttnExtra extra, cudaStream_t stream) {
     if (num_tokens <= 0 || num_requests <= 0) return TFF_OK;
+    if (extra.softcap < 0.f) return TFF_ERR_BAD_ARGUMENT;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_q_len <= 0 || num_splits < 1)
         return TFF_ERR_BAD_ARGUMENT;
     if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
@@ -436,6 +447,9 @@ static int attention_bf16_impl(
     p.nq = nq; p.nkv = nkv;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
+    p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
+    p.sink = extra.sink; p.gate = extra.gate;
     const bool keys_mode = (long long)max_q_len * G <= 16;
     const int block_m = keys_mode ? 16 : 64;
     const int q_tiles = (max_q_len * G + block_m - 1) / block_m;
@@ -443,11 +457,11 @@ static int attention_bf16_impl(
     if (keys_mode && cache_pages > 0)      // decode: keys streamed by TMA (attention_decode.cu), when it takes the shape
         st = tff_attention_decode_launch(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages,
                                          cache_layers, layer, page_size, out, p.part_o, p.part_ml, num_requests,
-                                         max_q_len, num_splits, nq, nkv, d, scale, window, stream);
+                                         max_q_len, num_splits, nq, nkv, d, scale, window, extra, stream);
     if (!keys_mode && num_splits == 1 && cache_pages > 0)   // portions: tcgen05 kernel (attention_prefill.cu)
         st = tff_attention_prefill_launch(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages,
                                           cache_layers, layer, page_size, out, num_requests, max_q_len, nq, nkv, d,
-                                          scale, window, stream);
+                                          scale, window, extra, stream);
     if (st == TFF_ERR_UNSUPPORTED) {
         if (d == 128) st = keys_mode ? launch_attn<128, true>(p, q_tiles, num_requests, stream)
                                      : launch_attn<128, false>(p, q_tiles, num_requests, stream);
@@ -459,9 +473,10 @@ static int attention_bf16_impl(
         const dim3 cgrid((unsigned)(nq * max_q_len), (unsigned)num_requests);
         if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, stream,
                                             (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits,
-                                            q_start, req_ids, nq);
+                                            q_start, req_ids, nq, extra.sink, extra.gate);
         return tff_launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, stream,
-                              (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits, q_start, req_ids, nq);
+                              (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits, q_start, req_ids, nq,
+                              extra.sink, extra.gate);
     }
     return TFF_OK;
 }
@@ -473,7 +488,7 @@ TFF_API int tff_attention_bf16(
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     return attention_bf16_impl(q, q_start, pos_start, nullptr, block_table, table_width, cache, 0, cache_layers, layer,
                                page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq, nkv, d,
-                               scale, window, stream);
+                               scale, window, AttnExtra{0.f, 0, nullptr}, stream);
 }
 
 // The same with the number of pages of the cache tensor given, which lets decode-sized calls
@@ -487,7 +502,18 @@ TFF_API int tff_attention_bf16_paged(
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     return attention_bf16_impl(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages, cache_layers,
                                layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
-                               nkv, d, scale, window, stream);
+                               nkv, d, scale, window, AttnExtra{0.f, 0, nullptr}, stream);
+}
+
+// The same with a cap on the scores, a sink in the softmax and a multiplier per (token, head) (attention_common.h).
+TFF_API int tff_attention_bf16_paged_ext(
+    const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
+    const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
+    void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
+    int nq, int nkv, int d, float scale, int window, float softcap, int sink, const float* gate, cudaStream_t stream) {
+    return attention_bf16_impl(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages, cache_layers,
+                               layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
+                               nkv, d, scale, window, AttnExtra{softcap, sink, gate}, stream);
 }
 
 // ------------------------------------------------------- allocation-free variant

@@ -68,6 +68,7 @@ struct DecodeParams {
     int cache_layers, layer, page_shift;         // page_size = 1 << page_shift
     bf16* out; float* part_o; float* part_ml; int num_splits;
     int nq, nkv; float scale_log2; int window;
+    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
     int* error_flag;
 };
 
@@ -242,7 +243,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
                 const int n = nbase + nt * 8 + (e & 1);
                 const bool up = e < 2;
                 const bool ok = up ? (v0 && n <= pr0 && n >= lo0) : (v1 && n <= pr1 && n >= lo1);
-                const float x = ok ? sc[nt][e] * p.scale_log2 : -INFINITY;
+                const float x = ok ? attn_score_log2(sc[nt][e], p.scale_log2, p.scale_over_cap, p.cap_log2) : -INFINITY;
                 sc[nt][e] = x;
                 if (up) bm0 = fmaxf(bm0, x); else bm1 = fmaxf(bm1, x);
             }
@@ -323,7 +324,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
         }
         const size_t grow = (size_t)(q0 + r / G) * p.nq + (kvh * G + r % G);
         if (p.num_splits == 1) {
-            p.out[grow * D + c] = __float2bfloat16_rn(acc / lsum);
+            if (p.sink) lsum += exp2f(-Ms);                        // the sink: a key of score 0
+            const float gt = p.gate ? p.gate[grow] : 1.f;
+            p.out[grow * D + c] = __float2bfloat16_rn(acc * gt / lsum);
         } else {
             p.part_o[(grow * p.num_splits + split) * D + c] = acc;
             if (c == 0) {
@@ -355,7 +358,7 @@ int tff_attention_decode_launch(
     const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, float* part_o, float* part_ml, int num_requests, int max_q_len, int num_splits,
-    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    int nq, int nkv, int d, float scale, int window, AttnExtra extra, cudaStream_t stream) {
     if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TFF_ERR_UNSUPPORTED;
     if ((long long)max_q_len * (nq / nkv) > 16 || cache_pages <= 0) return TFF_ERR_UNSUPPORTED;
@@ -372,6 +375,9 @@ int tff_attention_decode_launch(
     p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
     p.out = (bf16*)out; p.part_o = part_o; p.part_ml = part_ml; p.num_splits = num_splits;
     p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
+    p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
+    p.sink = extra.sink; p.gate = extra.gate;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     return d == 128 ? launch_decode<128>(tm, p, num_requests, stream) : launch_decode<64>(tm, p, num_requests, stream);

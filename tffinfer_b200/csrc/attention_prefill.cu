@@ -166,6 +166,7 @@ struct PrefillParams {
     int cache_layers, layer, page_shift;
     bf16* out;
     int nq, nkv; float scale_log2; int window;
+    float scale_over_cap, cap_log2; int sink; const float* gate;   // AttnExtra, ready for the kernel
     int* error_flag;
 };
 
@@ -449,7 +450,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
                 }
             }
             const float m_raw = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            const float m_blk = m_raw * p.scale_log2;
+            // (a cap is monotonic like the scale: the capped maximum is the cap of the raw one)
+            const float m_blk = m_raw == -INFINITY ? -INFINITY
+                                                   : attn_score_log2(m_raw, p.scale_log2, p.scale_over_cap, p.cap_log2);
             // lazy rescale: only when the maximum has grown by more than the threshold (warp-uniform decision)
             const bool grow = m_blk > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_blk > -INFINITY);
             // the product of the block before last must have read the P buffer that this block writes
@@ -492,7 +495,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
             uint8_t* prow = gP + (x * 2 + (j & 1)) * P_BYTES + r * 128;
             // scale, subtraction and the row's sum work on pairs of float32 (one instruction a pair)
             uint64_t lsum2[2] = {0ull, 0ull};
-            const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negms2 = pack2(-ms, -ms);
+            const bool capped = p.cap_log2 > 0.f;
+            // with a cap, the scores become tanh(s * scale / cap) first and the multiplier of the exponent cap * log2(e)
+            const uint64_t scale2 = capped ? pack2(p.cap_log2, p.cap_log2) : pack2(p.scale_log2, p.scale_log2),
+                           negms2 = pack2(-ms, -ms);
+            if (capped) {
+#pragma unroll
+                for (int i = 0; i < BLOCK_N; ++i)                  // a masked score stays masked
+                    s[i] = s[i] == -INFINITY ? -INFINITY : attn_tanh(s[i] * p.scale_over_cap);
+            }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
@@ -532,7 +543,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
         if (ok && nb_x > 0) ok = mbar_wait_warp(pv_done(x, (nb_x - 1) & 1), (uint32_t)((nb_x - 1) >> 1) & 1, abort_flag);
         if (ok && nb_x > 0) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            if (p.sink && l > 0.f) l += exp2f(-m_used);            // the sink: a key of score 0
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (p.gate && rv) inv *= p.gate[(size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)];
             bf16* orow = p.out + ((size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 16) {
@@ -596,7 +609,8 @@ TFF_API int tff_debug_ap_pair_timers(long long* out) {
 int tff_attention_prefill_launch(
     const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
-    void* out, int num_requests, int max_q_len, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    void* out, int num_requests, int max_q_len, int nq, int nkv, int d, float scale, int window, AttnExtra extra,
+    cudaStream_t stream) {
     if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TFF_ERR_UNSUPPORTED;
     if (cache_pages <= 0 || !(scale > 0.f)) return TFF_ERR_UNSUPPORTED;     // the kernel folds a positive scale into the exponent
@@ -613,6 +627,9 @@ int tff_attention_prefill_launch(
     p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
     p.out = (bf16*)out;
     p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.scale_over_cap = extra.softcap > 0.f ? scale / extra.softcap : 0.f;
+    p.cap_log2 = extra.softcap > 0.f ? extra.softcap * 1.4426950408889634f : 0.f;
+    p.sink = extra.sink; p.gate = extra.gate;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     const int G = nq / nkv;

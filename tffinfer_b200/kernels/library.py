@@ -572,6 +572,11 @@ class CudaKernels:
         assert tuple(q.shape) == (T, nq * d) and tuple(out.shape) == (T, nq * dv)
         assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, dc) and dc >= max(d, dv)
         assert gates is None or (gates.dtype == torch.float32 and tuple(gates.shape) == (T, nq))
+        if q.dtype == torch.bfloat16 and d == dv == dc and d in (64, 128) and hasattr(batch, "h_sorted_q_lens"):
+            # the kernels of plain attention take the cap, the sink and the gates as well
+            self.attention_bf16(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window,
+                                extra=(float(softcap), bool(sink), gates))
+            return
         c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         self._check(self.lib.tff_attention_generic_ext(
             _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]),
@@ -787,10 +792,11 @@ class CudaKernels:
         return self.attention_splits(eff, max_q_len, nq, nkv)
 
     def attention_bf16(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
-                       nq, nkv, d, scale, window, num_splits=None) -> None:
+                       nq, nkv, d, scale, window, num_splits=None, extra=(0.0, False, None)) -> None:
         """Flash attention over the paged cache (head sizes 64 and 128).  Requests that bring so few
         tokens that they fit a 16-row tile (decoded tokens) and requests that bring long portions are
-        launched apart when a step holds both, each with the kernel made for it."""
+        launched apart when a step holds both, each with the kernel made for it.  ``extra`` = (softcap, sink,
+        gates): a cap on the scores, a sink in the softmax, a float32 [T, nq] multiplier of the heads' outputs."""
         G = nq // nkv
         sq = batch.h_sorted_q_lens
         B = batch.num_requests
@@ -812,18 +818,18 @@ class CudaKernels:
             long_kv = int(batch.h_sorted_kv_lens[n_short:].max()) if batch.h_sorted_kv_lens is not None else 0
             shares = self.portion_splits(B - n_short, int(sq[-1]), long_kv, nq, nkv) if long_kv >= self.MIXED_SHARES_FROM else 1
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, shares, batch.req_order[n_short:], B - n_short, int(sq[-1]))
+                                        window, shares, batch.req_order[n_short:], B - n_short, int(sq[-1]), extra)
             splits = self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv)
             if side is None:
                 self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d,
                                             scale, window, splits, batch.req_order[:n_short], n_short,
-                                            int(sq[n_short - 1]))
+                                            int(sq[n_short - 1]), extra)
             else:
                 side.wait_event(self._fork)
                 with torch.cuda.stream(side):
                     self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv,
                                                 d, scale, window, splits, batch.req_order[:n_short], n_short,
-                                                int(sq[n_short - 1]))
+                                                int(sq[n_short - 1]), extra)
                     self._join.record(side)
                 main.wait_event(self._join)
         else:
@@ -835,10 +841,10 @@ class CudaKernels:
             # decoded tokens only: longest contexts first (the order the batch was packed with)
             order = batch.req_order if n_short == B else None
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, num_splits, order, B, batch.max_q_len)
+                                        window, num_splits, order, B, batch.max_q_len, extra)
 
     def _attention_bf16_launch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                               window, num_splits, req_ids, num_requests, max_q_len) -> None:
+                               window, num_splits, req_ids, num_requests, max_q_len, extra=(0.0, False, None)) -> None:
         T = q.shape[0]
         splits = num_splits
         c_ptr, c_pages, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
@@ -854,13 +860,15 @@ class CudaKernels:
                     self._portion_ws = ws
             else:
                 ws = torch.empty(need, dtype=torch.float32, device=q.device)
-        self._check(self.lib.tff_attention_bf16_paged(
+        softcap, sink, gates = extra
+        self._check(self.lib.tff_attention_bf16_paged_ext(
             _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(req_ids), _ptr(block_table),
             _c_int(block_table.shape[1]),
             c_ptr, ctypes.c_longlong(c_pages), _c_int(c_layers), _c_int(c_layer),
             _c_int(page_size),
             _ptr(out), _ptr(ws), _c_int(T), _c_int(num_requests), _c_int(max_q_len), _c_int(splits),
-            _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), self._stream()), "attention_bf16")
+            _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), _c_float(softcap),
+            _c_int(1 if sink else 0), _ptr(gates), self._stream()), "attention_bf16")
         self.launches += 2 if splits > 1 else 1
 
     def attention_generic(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
