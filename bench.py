@@ -414,12 +414,149 @@ def run_attn_decode(iters: int = 50) -> int:
     return 0
 
 
+# ------------------------------------------------------------------ the Tipezen design beside Qwen3 at equal layer sizes
+# (width, query heads, key/value heads, head size, feed-forward, window, retention heads) of two sizes that resemble a
+# real model's layers; the Tipezen model alternates retention layers without a feed-forward and attention layers with
+# one, over four residual streams; its twin is Qwen3 with as many layers of the same width, heads and feed-forward.
+TIPEZEN_SIZES = {"2k": (2048, 16, 4, 128, 6144, 1024, 16), "4k": (4096, 32, 8, 128, 12288, 2048, 32)}
+TIPEZEN_LAYERS = 8
+TIPEZEN_VOCAB = 32768
+
+
+def tipezen_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, step_tokens: int):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config import TipezenConfig, TipezenLayer, RotaryConfig
+    from tffinfer_b200.weights import random_tensors_on_device
+    W, H, G, D, F, win, RH = TIPEZEN_SIZES[size]
+    att = TipezenLayer(type="attention", heads=H, kv_heads=G, dim=D, vdim=D, scale=D ** -0.5, softcap=30.0, window=win,
+                       v_mix=True, rot=RotaryConfig(1e4, D, (8.0, 2048.0, 32.0, 1.0)), ff=F)
+    ret = TipezenLayer(type="retention", heads=RH, dim=D, vdim=D, rot=RotaryConfig(1e6, D),
+                       decay=tuple(1.0 - 2.0 ** (-5 - 4 * i / RH) for i in range(RH)))
+    cfg = TipezenConfig("Tipezen", vocab_size=TIPEZEN_VOCAB, hidden_size=W, streams=4, norm_eps=1e-6,
+                        layers=tuple(ret if i % 2 == 0 else att for i in range(TIPEZEN_LAYERS)))
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens, max_live_requests=max_live,
+                            max_tokens_per_step=step_tokens, max_model_len=8192, use_cuda_graphs=graphs)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def qwen_twin_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, step_tokens: int):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config import Qwen3Config
+    from tffinfer_b200.weights import random_tensors_on_device
+    W, H, G, D, F, win, _ = TIPEZEN_SIZES[size]
+    cfg = Qwen3Config(architecture="Qwen3ForCausalLM", hidden_size=W, num_layers=TIPEZEN_LAYERS, num_heads=H, num_kv_heads=G,
+                      head_dim=D, intermediate_size=F, vocab_size=TIPEZEN_VOCAB, rms_norm_eps=1e-6, rope_theta=1e6,
+                      max_position=8192, tie_word_embeddings=False, sliding_window=win,
+                      layer_types=tuple("sliding_attention" if i % 2 else "full_attention" for i in range(TIPEZEN_LAYERS))).validate()
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens, max_live_requests=max_live,
+                            max_tokens_per_step=step_tokens, max_model_len=8192, use_cuda_graphs=graphs)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def traced_kinds(engine, prompt_len: int, batch: int):
+    """Device time by kind of kernel call of one whole-prompt step and of one decode step of ``batch`` requests
+    behind such prompts, launched kernel by kernel (the engine was made without CUDA graphs)."""
+    import torch
+    from tffinfer_b200 import StepEntry
+    from tffinfer_b200.kernels.trace import KernelTrace
+    runner = engine.runner
+    rng = random.Random(3)
+    vocab = runner.desc.vocab_size
+    ids = [f"t{i}" for i in range(batch)]
+    for rid in ids:
+        runner.add_request(rid)
+    prompt = lambda: [rng.randrange(vocab) for _ in range(prompt_len)]
+    out = {}
+    runner.step([StepEntry(ids[0], prompt(), [prompt_len - 1])])            # every prompt-sized kernel has run once
+    torch.cuda.synchronize()
+    with KernelTrace(runner.ops) as tr:
+        runner.step([StepEntry(ids[1], prompt(), [prompt_len - 1])])
+    out["prefill"] = {k: (c, round(ms, 4)) for k, c, ms in tr.summary()}
+    for rid in ids[2:]:
+        runner.step([StepEntry(rid, prompt(), [])])
+    runner.step([StepEntry(rid, [1], [0]) for rid in ids])                   # and every decode-sized one
+    torch.cuda.synchronize()
+    with KernelTrace(runner.ops) as tr:
+        runner.step([StepEntry(rid, [2], [0]) for rid in ids])
+    out["decode"] = {k: (c, round(ms, 4)) for k, c, ms in tr.summary()}
+    for rid in ids:
+        runner.finish_request(rid)
+    return out
+
+
+def run_tipezen(steps: int, warmup: int) -> int:
+    """Prefill and decode throughput of the Tipezen design at two layer sizes beside Qwen3 at the same sizes, one JSON
+    line a point, and for each model the device time of a step by kind of kernel call with what the new kernels
+    reach of the measured copy rate (streams, rotation and cache write, decode retention) or of the float32 FMA
+    rate of the device (chunked retention)."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 32)
+    P = PROMPT_LEN
+    for size in TIPEZEN_SIZES:
+        W, H, G, D, F, win, RH = TIPEZEN_SIZES[size]
+        for model, make in (("tipezen", tipezen_engine), ("qwen3", qwen_twin_engine)):
+            need = 64 * (P + warmup + steps + 64 + 72)
+            engine, cfg = make(size, 64, need, True, P)
+            pms = prefill_run(engine, iters=3, warmup=2, seed=1, prompt_len=P)
+            print(json.dumps({"point": "prefill", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "tokens": P,
+                              "ms": round(pms, 3), "tok_s": round(P / (pms / 1e3), 1)}), flush=True)
+            for b in (8, 64):
+                run = decode_run(engine, b, steps, warmup, seed=b, prompt_len=P)
+                print(json.dumps({"point": "decode", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "batch": b,
+                                  "context": round(run["mean_context"]), "tok_s": round(run["tok_s"], 1),
+                                  "ms_per_step": round(run["ms_per_step"], 4), "launches_per_step": run["launches"] // steps}),
+                      flush=True)
+            del engine
+            torch.cuda.empty_cache()
+            engine, cfg = make(size, 8, 8 * (P + 64), False, P)
+            kinds = traced_kinds(engine, P, 8)
+            line = {"point": "kernels", "model": model, "size": size, "prefill_tokens": P, "decode_batch": 8,
+                    "prefill_ms_by_kind": kinds.get("prefill"), "decode_ms_by_kind": kinds.get("decode"), "peaks": peaks["source"]}
+            if model == "tipezen":
+                nl = TIPEZEN_LAYERS // 2
+                S = 4
+                # bytes a call must move, summed over the step's calls of the kind
+                subl = nl * 3                                  # sublayers: a mixer a layer, a feed-forward every other
+                stream_b = lambda T: (subl + 1) * T * (2 * S * W * 4 + W * 4 + W * 2)
+                finish_b = lambda T: nl * T * ((2 * RH * D + 2 * RH * D) * 4 + (2 * RH * D) * 4) + \
+                    nl * T * ((H + 2 * G) * D * 4 + H * D * 2 + 2 * G * D * 2 + 2 * G * D * 4)
+                state_b = nl * 8 * RH * D * D * 4 * 2          # decode: every request's state read and written
+                ret_flops = lambda T: nl * RH * T * 2.0 * (D * D * 2 + 32 * D + 32 * D / 2.0 + D * D)   # chunks of 32
+                fr = {}
+                for step, T in (("prefill", P), ("decode", 8)):
+                    k = kinds.get(step) or {}
+                    if "stream_step" in k:
+                        fr[f"{step}_stream_step_hbm_frac"] = round(stream_b(T) / (k["stream_step"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                    if "qkv_finish" in k:
+                        fr[f"{step}_qkv_finish_hbm_frac"] = round(finish_b(T) / (k["qkv_finish"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                if "retention" in (kinds.get("decode") or {}):
+                    fr["decode_retention_hbm_frac"] = round(state_b / (kinds["decode"]["retention"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                if "retention" in (kinds.get("prefill") or {}):
+                    fr["prefill_retention_fp32_tflops"] = round(ret_flops(P) / (kinds["prefill"]["retention"][1] / 1e3) / 1e12, 2)
+                line["fractions"] = fr
+            print(json.dumps(line), flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
                          "context lengths; attn_decode: the decode attention alone; shapes: the layer sizes of the other "
-                         "models of the family; else a whole workload through "
+                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; else a whole workload through "
                          "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -448,6 +585,8 @@ def main() -> int:
         return run_attn_decode()
     if args.workload == "shapes":
         return run_shapes(args.steps, warmup)
+    if args.workload == "tipezen":
+        return run_tipezen(args.steps, warmup)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 

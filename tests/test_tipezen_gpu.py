@@ -286,15 +286,7 @@ def test_retention_steps_chunks_and_far_keys(ops, H, d, dv):
         qq, kk = cat(q).reshape(-1, H * d).cuda(), cat(k).reshape(-1, H * d).cuda()
         vg = torch.cat([cat(v).reshape(-1, H * dv), cat(gate)], dim=1).cuda()
         out = torch.empty(qq.shape[0], H * dv, device="cuda")
-        chunked = 0 if max(lens) == 1 else 1
-        from tffinfer_b200.kernels.library import _ptr, _c_int, _c_float
-        args = lambda ch: (_ptr(qq), _ptr(kk), _ptr(vg), _c_int(vg.shape[1]), _c_int(0), _c_int(H * dv), _ptr(state),
-                           _c_int(5), _ptr(b.q_start), _ptr(b.pos_start), _ptr(b.slots), _ptr(dec), _ptr(out), _c_int(0),
-                           _c_int(len(live)), _c_int(H), _c_int(d), _c_int(dv), _c_float(1e-6), _c_int(ch), ops._stream())
-        st = ops.lib.tff_retention(*args(chunked))
-        if st == -2:
-            st = ops.lib.tff_retention(*args(0))
-        assert st == 0
+        ops.retention(qq, kk, vg, 0, H * dv, state, b, dec, out, H, d, dv, 1e-6)
         row = 0
         for r in live:
             got[r][done[r]:done[r] + lens[r]] = out[row:row + lens[r]].cpu()

@@ -9,7 +9,17 @@ namespace tc5 {
 // alternate between 64 gate and 64 up features (normal orientation, bfloat16 out, through TMA)
 // EPI_QKV: the product is a q/k/v projection with heads of 128: per-head RMSNorm of q and k, rotation, q to its
 // own tensor and k, v to the token's slot of the paged cache (epilogue_quarter_qkv below)
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+// EPI_GEGLU: as EPI_SWIGLU with the tanh form of gelu on the gate, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
+// which is g / (1 + exp(-2 sqrt(2/pi) (g + 0.044715 g^3))): the same exponential and division as silu
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GEGLU = 4 };
+__host__ __device__ constexpr bool epi_gated(int e) { return e == EPI_SWIGLU || e == EPI_GEGLU; }
+
+// act(g) of the gated epilogues with the fast exponential and division (the result is rounded to bfloat16)
+template <int EPI>
+__device__ __forceinline__ float gate_act_fast(float g) {
+    if constexpr (EPI == EPI_GEGLU) return __fdividef(g, 1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+    else return __fdividef(g, 1.0f + __expf(-g));
+}
 
 // One warp's quarter (32 rows) of the tile: TMEM -> registers -> two alternating 4 KB boxes of swizzled
 // shared memory (``my_stage``) -> TMA stores, or float32 add-reductions when the product is added to what
@@ -20,7 +30,7 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
                                                      int lane_row0, int col_row0, bool partial, const CUtensorMap* tm_out) {
     // 128-byte-wide column chunks: 32 float32 or 64 bfloat16 per row
     constexpr int CW = 128 / (int)sizeof(TC);      // output columns per chunk
-    constexpr int AW = EPI == EPI_SWIGLU ? 128 : CW;   // accumulator columns per chunk
+    constexpr int AW = epi_gated(EPI) ? 128 : CW;   // accumulator columns per chunk
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += AW, ++chunk_no) {
         const uint32_t buf = my_stage + (chunk_no & 1) * 4096u;
@@ -29,7 +39,7 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
             __syncwarp();
         }
         uint32_t packed[32];                       // this thread's row: 128 bytes
-        if constexpr (EPI == EPI_SWIGLU) {
+        if constexpr (epi_gated(EPI)) {
             // columns [c0, c0+64) are the gate, [c0+64, c0+128) the up projection of the
             // same 64 features: silu(g) * u, silu(g) = g / (1 + exp(-g)).  The division is the fast one (the result
             // is rounded to bfloat16): the exact one takes its slow path for a numerator of zero, which is what every
@@ -43,8 +53,8 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-                    const float a0 = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]);
-                    const float a1 = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+                    const float a0 = gate_act_fast<EPI>(g0) * __uint_as_float(u[2 * j]);
+                    const float a1 = gate_act_fast<EPI>(g1) * __uint_as_float(u[2 * j + 1]);
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(a0, a1);
                     packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
                 }
@@ -76,7 +86,7 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-            if (EPI == EPI_SWIGLU) tma_store_2d(tm_out, buf, (col_row0 + c0) / 2, lane_row0 + q * 32);
+            if (epi_gated(EPI)) tma_store_2d(tm_out, buf, (col_row0 + c0) / 2, lane_row0 + q * 32);
             else if (EPI == EPI_ADD || partial) tma_reduce_add_2d(tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
             else tma_store_2d(tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
             bulk_commit();

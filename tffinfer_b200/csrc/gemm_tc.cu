@@ -381,9 +381,9 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
 // blocks of 64: rows [128 b, 128 b + 64) = gate features [64 b, 64 b + 64), rows [128 b + 64, 128 b + 128)
 // = the same up features.  Normal orientation only (prompt-sized M); I must be a multiple of 64.
 // TFF_ERR_UNSUPPORTED for shapes it does not take.
-TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, int I, int K, int bn, cudaStream_t stream) {
+static int gemm_tc_gated(const void* A, const void* W, void* out, int M, int I, int K, int bn, int act, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return TFF_OK;
-    if (K <= 0) return TFF_ERR_BAD_ARGUMENT;
+    if (K <= 0 || (act != 0 && act != 1)) return TFF_ERR_BAD_ARGUMENT;
     if (K % 8 != 0 || I % 64 != 0 || (bn != 128 && bn != 256 && bn != 512)) return TFF_ERR_UNSUPPORTED;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
     if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
@@ -392,10 +392,24 @@ TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, i
     if (bn == 512) {                                  // 256 x 256 tiles on pairs of SMs
         if (!tff_tensor_map_2d(W, 2ll * I, K, 128, BK, 2, &tc)) return TFF_ERR_DRIVER;
         if (!tff_tensor_map_2d(out, M, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
-        return tff_gemm_tc_pair_launch(tl, tc, to, EPI_SWIGLU, 1, M, 2 * I, K, 0, stream);
+        return tff_gemm_tc_pair_launch(tl, tc, to, act ? EPI_GEGLU : EPI_SWIGLU, 1, M, 2 * I, K, 0, stream);
     }
     if (!tff_tensor_map_2d(W, 2ll * I, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
     if (!tff_tensor_map_2d(out, M, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
+    if (act) {
+        if (bn == 256) return launch_tc<256, false, EPI_GEGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
+        return launch_tc<128, false, EPI_GEGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
+    }
     if (bn == 256) return launch_tc<256, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
     return launch_tc<128, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
+}
+
+TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, int I, int K, int bn, cudaStream_t stream) {
+    return gemm_tc_gated(A, W, out, M, I, K, bn, 0, stream);
+}
+
+// The same with the gate's activation chosen: act 0 = silu, 1 = gelu (tanh form).
+TFF_API int tff_gemm_tc_gated(const void* A, const void* W, void* out, int M, int I, int K, int bn, int act,
+                              cudaStream_t stream) {
+    return gemm_tc_gated(A, W, out, M, I, K, bn, act, stream);
 }

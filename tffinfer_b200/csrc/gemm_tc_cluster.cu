@@ -60,6 +60,7 @@ struct ClusterGemmParams {
     const float* norm_w; float eps;       // FOLD_NORM: input RMSNorm
     int M, N, K;
     bf16* act; int inter;                 // [M, inter] bfloat16 out
+    int gelu;                             // the gate's activation: 0 silu, 1 gelu (tanh form)
     int* error_flag;
 };
 
@@ -327,7 +328,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             if (channel >= p.inter) continue;
             const float r = FOLD_NORM ? rsqrtf(sumsq[j] * inv_k + p.eps) : 1.0f;
             const float g = red[c * BN + j] * r, u = red[(64 + c) * BN + j] * r;
-            p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // rounded to bfloat16 anyway
+            const float e = p.gelu ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;      // gelu (tanh form) or silu
+            p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-e)) * u);   // rounded to bfloat16 anyway
         }
     }
     // ------------------------------------------------------------------ teardown
@@ -381,15 +383,15 @@ int launch_cluster_gemm(const CUtensorMap& tw, const CUtensorMap& th, const Clus
 // gate/up projection of a decode step of at most 16 tokens with the norm ahead of it and its activation:
 // act [M, I] bfloat16 = silu(gate) * up of RMSNorm(x) W^T; x [M, K] float32, W [2 I, K] bfloat16 with gate and up
 // rows alternating in blocks of 64 (I a multiple of 64).  TFF_ERR_UNSUPPORTED for shapes it does not take.
-TFF_API int tff_gemm_tc_cluster_swiglu(const float* x, const float* norm_w, float eps, const void* W, int M, int K,
-                                       void* act, int inter, cudaStream_t stream) {
+static int cluster_gated_norm(const float* x, const float* norm_w, float eps, const void* W, int M, int K,
+                              void* act, int inter, int gelu, cudaStream_t stream) {
     if (M <= 0) return TFF_OK;
     if (inter <= 0 || !act || K <= 0 || !x || !norm_w || !W) return TFF_ERR_BAD_ARGUMENT;
     if (inter % 64 != 0 || M > 16 || K % 8 != 0) return TFF_ERR_UNSUPPORTED;
     if (((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)norm_w & 15)) return TFF_ERR_UNSUPPORTED;
     ClusterGemmParams p = {};
     p.x = x; p.norm_w = norm_w; p.eps = eps; p.M = M; p.N = 2 * inter; p.K = K;
-    p.act = (bf16*)act; p.inter = inter;
+    p.act = (bf16*)act; p.inter = inter; p.gelu = gelu;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     CUtensorMap tw;
@@ -397,20 +399,42 @@ TFF_API int tff_gemm_tc_cluster_swiglu(const float* x, const float* norm_w, floa
     return launch_cluster_gemm<16, true>(tw, tw, p, stream);
 }
 
+TFF_API int tff_gemm_tc_cluster_swiglu(const float* x, const float* norm_w, float eps, const void* W, int M, int K,
+                                       void* act, int inter, cudaStream_t stream) {
+    return cluster_gated_norm(x, norm_w, eps, W, M, K, act, inter, 0, stream);
+}
+
 // The same for activation rows that have been normalised already: h [M <= 16, K] bfloat16.
-TFF_API int tff_gemm_tc_cluster_swiglu_bf16(const void* h, const void* W, int M, int K, void* act, int inter,
-                                            cudaStream_t stream) {
+static int cluster_gated_bf16(const void* h, const void* W, int M, int K, void* act, int inter, int gelu,
+                              cudaStream_t stream) {
     if (M <= 0) return TFF_OK;
     if (inter <= 0 || !act || K <= 0 || !h || !W) return TFF_ERR_BAD_ARGUMENT;
     if (inter % 64 != 0 || M > 16 || K % 8 != 0) return TFF_ERR_UNSUPPORTED;
     if (((uintptr_t)W & 15) || ((uintptr_t)h & 15)) return TFF_ERR_UNSUPPORTED;
     ClusterGemmParams p = {};
     p.M = M; p.N = 2 * inter; p.K = K;
-    p.act = (bf16*)act; p.inter = inter;
+    p.act = (bf16*)act; p.inter = inter; p.gelu = gelu;
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     CUtensorMap tw, th;
     if (!tff_tensor_map_2d(W, p.N, K, BM, BK, 2, &tw)) return TFF_ERR_DRIVER;
     if (!tff_tensor_map_2d(h, M, K, 16, BK, 2, &th)) return TFF_ERR_DRIVER;     // rows beyond M arrive as zeros
     return launch_cluster_gemm<16, false>(tw, th, p, stream);
+}
+
+TFF_API int tff_gemm_tc_cluster_swiglu_bf16(const void* h, const void* W, int M, int K, void* act, int inter,
+                                            cudaStream_t stream) {
+    return cluster_gated_bf16(h, W, M, K, act, inter, 0, stream);
+}
+
+// Both with the gate's activation chosen: act 0 = silu, 1 = gelu (tanh form).
+TFF_API int tff_gemm_tc_cluster_gated(const float* x, const float* norm_w, float eps, const void* W, int M, int K,
+                                      void* act, int inter, int gate_act, cudaStream_t stream) {
+    if (gate_act != 0 && gate_act != 1) return TFF_ERR_BAD_ARGUMENT;
+    return cluster_gated_norm(x, norm_w, eps, W, M, K, act, inter, gate_act, stream);
+}
+TFF_API int tff_gemm_tc_cluster_gated_bf16(const void* h, const void* W, int M, int K, void* act, int inter, int gate_act,
+                                           cudaStream_t stream) {
+    if (gate_act != 0 && gate_act != 1) return TFF_ERR_BAD_ARGUMENT;
+    return cluster_gated_bf16(h, W, M, K, act, inter, gate_act, stream);
 }

@@ -292,6 +292,7 @@ int tff_gemm_tc_pair_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_w_hal
                             int out_is_bf16, int M, int N, int K, int stream_k, cudaStream_t stream) {
     if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
     if (epilogue == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(tm_a, tm_w_half, tm_out, M, N, K, 0, stream);
+    if (epilogue == EPI_GEGLU) return launch_pair<EPI_GEGLU, bf16>(tm_a, tm_w_half, tm_out, M, N, K, 0, stream);
     if (out_is_bf16) {
         if (epilogue != EPI_STORE || stream_k) return TFF_ERR_BAD_ARGUMENT;
         return launch_pair<EPI_STORE, bf16>(tm_a, tm_w_half, tm_out, M, N, K, 0, stream);

@@ -8,7 +8,8 @@
 //   tm_a        A as [M, K], box 64 x 128
 //   tm_w_half   W as [N, K], box 64 x 128 (each CTA of a pair loads half of the tile's 256 rows)
 //   tm_out      out, boxes of 128 bytes x 32 rows
-//   epilogue    0 store, 1 add to what out (float32) holds, 2 SwiGLU of interleaved gate/up columns (bfloat16 out)
+//   epilogue    0 store, 1 add to what out (float32) holds, 2 SwiGLU of interleaved gate/up columns (bfloat16 out),
+//               4 the same with gelu (tanh form) on the gate
 //   stream_k    0, or S >= 1: the tiles of the last wave in S slices of their K range (float32 out that holds
 //               the initial value)
 // Returns a TFF_* status.

@@ -10,6 +10,9 @@
 //   unrounded, in v_share [T, nkv*dv] float32.  2: v <- (1 - lambda) v + lambda v_share[t], lambda a float32 scalar on
 //   the device.  The (mixed) v goes to the token's slot of the cache; without a cache v is left where it is.
 // * head gates: gate_out[t, h] = sigmoid(proj[t, gate_off + h]) for the nq query heads, when gate_out is given.
+// With ``clear_input`` every element of the row that the kernel has consumed is set to zero behind the read (q, k,
+// the gates, and v where there is a cache to take it): the row is then an accumulator buffer that the next split
+// product adds into.
 // The cache is [pages, layers, 2, kv heads, page, dc] with dc >= max(d, dv): keys use the first d elements of a
 // slot, values the first dv.
 // Everything is computed in float32; only the stores round.
@@ -19,7 +22,7 @@ namespace {
 
 template <typename TIN, typename TQ, typename TC>
 __global__ void __launch_bounds__(128)
-qkv_finish_kernel(const TIN* __restrict__ proj, int ld, TQ* __restrict__ q_out, float* __restrict__ k_out,
+qkv_finish_kernel(TIN* __restrict__ proj, int clear_input, int ld, TQ* __restrict__ q_out, float* __restrict__ k_out,
                   const float* __restrict__ freq, int rot_dims, float magnitude, int interleaved, float k_scale,
                   const int* __restrict__ positions, const int* __restrict__ tok_req,
                   const int* __restrict__ block_table, int table_width,
@@ -35,10 +38,12 @@ qkv_finish_kernel(const TIN* __restrict__ proj, int ld, TQ* __restrict__ q_out, 
     if (head >= heads) return;
     const int pos = positions[t];
     pdl_wait();
-    const TIN* row = proj + (size_t)t * ld;
+    TIN* row = proj + (size_t)t * ld;
+    const TIN zero = from_f32<TIN>(0.f);
     if (head == nq + 2 * nkv) {                                   // the head gates of this token
         for (int h = lane; h < nq; h += 32) {
             const float g = to_f32<TIN>(row[gate_off + h]);
+            if (clear_input) row[gate_off + h] = zero;
             gate_out[(size_t)t * nq + h] = 1.0f / (1.0f + expf(-g));
         }
         return;
@@ -54,23 +59,26 @@ qkv_finish_kernel(const TIN* __restrict__ proj, int ld, TQ* __restrict__ q_out, 
     }
     if (!is_q && !is_k) {                                         // a value head
         const int kvh = head - nq - nkv;
-        const TIN* src = row + (size_t)(nq + nkv) * d + (size_t)kvh * dv;
+        TIN* src = row + (size_t)(nq + nkv) * d + (size_t)kvh * dv;
+        if (!slot && v_mode != 1) return;                         // nobody takes the values here: they stay in the row
         float* share = v_share ? v_share + (size_t)t * nkv * dv + (size_t)kvh * dv : nullptr;
         const float lam = v_mode == 2 ? *lambda : 0.f;
         for (int i = lane; i < dv; i += 32) {
             float v = to_f32<TIN>(src[i]);
+            if (clear_input && slot) src[i] = zero;
             if (v_mode == 1) share[i] = v;
             else if (v_mode == 2) v = (1.0f - lam) * v + lam * share[i];
             if (slot) slot[i] = from_f32<TC>(v);
         }
         return;
     }
-    const TIN* src = row + (size_t)head * d;                      // q heads, then k heads, all of size d
+    TIN* src = row + (size_t)head * d;                            // q heads, then k heads, all of size d
     const int half = rot_dims >> 1;
     const float ks = is_q ? 1.f : k_scale;
     for (int i = lane; i < half; i += 32) {
         const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
         const float a = to_f32<TIN>(src[ia]), b = to_f32<TIN>(src[ib]);
+        if (clear_input) { src[ia] = zero; src[ib] = zero; }      // this lane alone reads these two
         float s, c;
         sincosf((float)pos * freq[i], &s, &c);
         s *= magnitude; c *= magnitude;
@@ -87,6 +95,7 @@ qkv_finish_kernel(const TIN* __restrict__ proj, int ld, TQ* __restrict__ q_out, 
     }
     for (int i = 2 * half + lane; i < d; i += 32) {
         const float a = to_f32<TIN>(src[i]) * ks;
+        if (clear_input) src[i] = zero;
         if (is_q) q_out[(size_t)t * nq * d + (size_t)head * d + i] = from_f32<TQ>(a);
         else if (slot) slot[i] = from_f32<TC>(a);
         else k_out[(size_t)t * nkv * d + (size_t)(head - nq) * d + i] = a;
@@ -97,7 +106,7 @@ qkv_finish_kernel(const TIN* __restrict__ proj, int ld, TQ* __restrict__ q_out, 
 
 // in_dt, q_dt, cache_dt: 0 = float32, 1 = bfloat16.  q_out has q_dt; the cache cache_dt; k_out and v_share are float32.
 TFF_API int tff_qkv_finish(
-    const void* proj, int in_dt, int ld, void* q_out, int q_dt, float* k_out,
+    void* proj, int in_dt, int clear_input, int ld, void* q_out, int q_dt, float* k_out,
     const float* freq, int rot_dims, float magnitude, int interleaved, float k_scale,
     const int* positions, const int* tok_req, const int* block_table, int table_width,
     void* cache, int cache_dt, int cache_layers, int layer, int page_size, int dc,
@@ -117,7 +126,7 @@ TFF_API int tff_qkv_finish(
     const int heads = nq + 2 * nkv + (gate_out ? 1 : 0);
     dim3 grid((heads + 3) / 4, num_tokens);
 #define TFF_FIN(TIN, TQ, TC)                                                                                       \
-    return tff_launch_pdl(qkv_finish_kernel<TIN, TQ, TC>, grid, dim3(128), 0, stream, (const TIN*)proj, ld, (TQ*)q_out,  \
+    return tff_launch_pdl(qkv_finish_kernel<TIN, TQ, TC>, grid, dim3(128), 0, stream, (TIN*)proj, clear_input, ld, (TQ*)q_out, \
                           k_out, freq, rot_dims, magnitude, interleaved, k_scale, positions, tok_req, block_table,   \
                           table_width, (TC*)cache, L, layer, dc, v_mode, v_share, lambda, gate_off, gate_out, nq,     \
                           nkv, d, dv)

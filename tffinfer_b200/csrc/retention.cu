@@ -8,14 +8,15 @@
 // state [slots, H, d, dv] float32; request b of the step uses slot slots[b] and brings the rows
 // q_start[b] .. q_start[b+1]-1.  Everything is float32 FMA.
 //
-// Two kernels.  The token-by-token one (a CTA per (head, request), the state in shared memory) is the decode
-// kernel: with one token a request it reads and writes the state once.  Portions of prompts run chunk by chunk:
-// within a chunk of C tokens
+// The token-by-token kernel (a CTA per (head, request), the state in shared memory) is the decode kernel: with one
+// token a request it reads and writes the state once.  Portions of prompts run chunk by chunk: within a chunk of n
+// tokens that starts from the state S_0
 //   o_i = decay^(i+1) S_0^T q_i + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j
-//   S_C = decay^C S_0 + sum_j decay^(C-1-j) k_j v_j^T
-// so the C tokens of a chunk are worked on side by side and the state is touched once a chunk.  Chunks are aligned
-// to absolute positions of the request (a chunk never crosses a multiple of C), so that the order of the
-// additions that make a token's output depends on its position alone, not on how the prompt was cut.
+//   S_n = decay^n S_0 + sum_j decay^(n-1-j) k_j v_j^T
+// so the tokens of a chunk, and all chunks of a step, are worked on side by side, and only a cheap pass per state
+// element walks the chunks in order.  Chunks are aligned to absolute positions of the request, so that the order of
+// the additions that make a token's output depends on its position (and on where a portion was cut), not on what
+// else is in the batch.
 #include "common.cuh"
 
 namespace {
@@ -23,7 +24,8 @@ namespace {
 constexpr int NT = 256;
 
 struct RetParams {
-    const float* q; const float* k; const float* vg; int ld, v_off, g_off;
+    const float* q; const float* k; float* vg; int ld, v_off, g_off;
+    int clear;                         // v and g are set to zero behind the read (the rows are an accumulator buffer)
     float* state; int num_slots;
     const int* q_start; const int* pos_start; const int* slots;
     const float* decay;                // [H] on the device
@@ -60,7 +62,10 @@ retention_step_kernel(RetParams p) {
             sq[i] = p.q[(size_t)t * p.H * d + (size_t)h * d + i];
             sk[i] = p.k[(size_t)t * p.H * d + (size_t)h * d + i];
         }
-        for (int i = threadIdx.x; i < dv; i += NT) sv[i] = p.vg[(size_t)t * p.ld + p.v_off + h * dv + i];
+        for (int i = threadIdx.x; i < dv; i += NT) {
+            sv[i] = p.vg[(size_t)t * p.ld + p.v_off + h * dv + i];
+            if (p.clear) p.vg[(size_t)t * p.ld + p.v_off + h * dv + i] = 0.f;
+        }
         __syncthreads();
         if (active) {
             float acc = 0.f;
@@ -79,6 +84,7 @@ retention_step_kernel(RetParams p) {
         if (threadIdx.x < dv) {
             const float rs = rsqrtf(ss / (float)dv + p.eps);
             const float g = p.vg[(size_t)t * p.ld + p.g_off + h * dv + threadIdx.x];
+            if (p.clear) p.vg[(size_t)t * p.ld + p.g_off + h * dv + threadIdx.x] = 0.f;
             ((TO*)p.out)[(size_t)t * p.H * dv + (size_t)h * dv + threadIdx.x] =
                 from_f32<TO>((o * rs) * (g / (1.0f + expf(-g))));
         }
@@ -88,132 +94,261 @@ retention_step_kernel(RetParams p) {
 }
 
 // ------------------------------------------------------------------ chunk by chunk
-// A CTA per (head, request).  Shared memory: the state [d][dv], and of the chunk q [C][d+1], k [C][d+1],
-// v [C][dv], the masked, decayed scores A [C][C+1] and the powers of the decay.
-constexpr int C = 32;
+// Portions of prompts.  A chunk is up to C tokens of one request that do not cross a multiple of C of the request's
+// positions.  Three kernels, the first and the last with a CTA per (chunk, head), so that all chunks of a prompt are
+// worked on at once:
+//   1. local:  A = mask(decay^(i-j) q_i . k_j);  acc = A V  (-> acc [T, H*dv]);  U = sum_j decay^(n-1-j) k_j v_j^T (-> U[chunk])
+//   2. scan:   per (request, head, state element), over the request's chunks in order: U[chunk] <- S (the state the
+//              chunk starts from), S <- decay^n S + U[chunk]; the last S goes back to the request's slot
+//   3. finish: o_i = acc_i + decay^(i+1) S^T q_i, then the head's RMS norm and the gate -> out
+// The products are float32 FMAs on 4 x 4 register tiles out of shared memory (operands zero-padded to multiples of 4).
+constexpr int C = 64;
+
+__host__ __device__ inline int pad4(int x) { return (x + 3) & ~3; }
+
+// Which chunk is CTA ``index``: request b, first row t, tokens n, position of the first token; false beyond the last.
+struct ChunkRef { int b, t, n, pos; };
+__device__ inline bool find_chunk(const RetParams& p, int num_requests, int index, ChunkRef& c) {
+    for (int b = 0; b < num_requests; ++b) {
+        const int t0 = p.q_start[b], len = p.q_start[b + 1] - t0;
+        if (len <= 0) continue;
+        const int pos0 = p.pos_start[b];
+        const int first = pos0 / C, count = (pos0 + len - 1) / C - first + 1;
+        if (index < count) {
+            const int lo = max(pos0, (first + index) * C), hi = min(pos0 + len, (first + index + 1) * C);
+            c.b = b; c.pos = lo; c.t = t0 + (lo - pos0); c.n = hi - lo;
+            return true;
+        }
+        index -= count;
+    }
+    return false;
+}
+
+// out(m, n) = sum_k A[m][k] B[k][n] for m < M, n < N; K a multiple of 4; rows of A up to pad4(M) and columns of B up
+// to pad4(N) are readable.  Consecutive threads take consecutive column tiles.
+template <typename F>
+__device__ __forceinline__ void tile_product(const float* __restrict__ A, int lda, const float* __restrict__ B, int ldb,
+                                             int M, int N, int K, F&& store) {
+    const int tn = (N + 3) >> 2, tm = (M + 3) >> 2;
+    for (int tile = threadIdx.x; tile < tm * tn; tile += NT) {
+        const int m0 = (tile / tn) << 2, n0 = (tile % tn) << 2;
+        float acc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+        for (int k = 0; k < K; k += 4) {
+            float4 a[4], b[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4*>(A + (m0 + r) * lda + k);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) b[kk] = *reinterpret_cast<const float4*>(B + (k + kk) * ldb + n0);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float av[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    acc[r][0] = fmaf(av[kk], b[kk].x, acc[r][0]);
+                    acc[r][1] = fmaf(av[kk], b[kk].y, acc[r][1]);
+                    acc[r][2] = fmaf(av[kk], b[kk].z, acc[r][2]);
+                    acc[r][3] = fmaf(av[kk], b[kk].w, acc[r][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (m0 + r < M && n0 + c < N) store(m0 + r, n0 + c, acc[r][c]);
+    }
+}
+
+__device__ __forceinline__ void fill_powers(float* pw, float decay) {
+    if (threadIdx.x == 0) { float x = 1.f; for (int i = 0; i <= C; ++i) { pw[i] = x; x *= decay; } }
+}
+
+__global__ void __launch_bounds__(NT)
+retention_local_kernel(RetParams p, int num_requests, float* __restrict__ acc, float* __restrict__ U) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float pw[C + 1];
+    pdl_launch_dependents();
+    const int h = blockIdx.y, d = p.d, dv = p.dv, dP = pad4(d), vP = pad4(dv);
+    float* sq = sm;                      // [C][dP]
+    float* skT = sq + C * dP;            // [dP][C]
+    float* sv = skT + dP * C;            // [C][vP]
+    float* sA = sv + C * vP;             // [C][C]
+    ChunkRef c;
+    const bool have = find_chunk(p, num_requests, blockIdx.x, c);
+    fill_powers(pw, p.decay[h]);
+    pdl_wait();
+    if (!have) return;
+    const int n = c.n, nP = pad4(n);
+    for (int e = threadIdx.x; e < C * dP + dP * C + C * vP + C * C; e += NT) sm[e] = 0.f;
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * d; e += NT) {
+        const int i = e / d, r = e % d;
+        sq[i * dP + r] = p.q[(size_t)(c.t + i) * p.H * d + (size_t)h * d + r];
+        skT[r * C + i] = p.k[(size_t)(c.t + i) * p.H * d + (size_t)h * d + r];
+    }
+    for (int e = threadIdx.x; e < n * dv; e += NT) {
+        const int i = e / dv, r = e % dv;
+        sv[i * vP + r] = p.vg[(size_t)(c.t + i) * p.ld + p.v_off + h * dv + r];
+        if (p.clear) p.vg[(size_t)(c.t + i) * p.ld + p.v_off + h * dv + r] = 0.f;
+    }
+    __syncthreads();
+    tile_product(sq, dP, skT, C, n, n, dP, [&](int i, int j, float a) { sA[i * C + j] = j <= i ? a * pw[i - j] : 0.f; });
+    __syncthreads();
+    tile_product(sA, C, sv, vP, n, dv, nP, [&](int i, int r, float a) {
+        acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + r] = a;
+    });
+    __syncthreads();                                                  // every thread is done with skT as it was
+    for (int e = threadIdx.x; e < d * n; e += NT) { const int r = e / n, j = e % n; skT[r * C + j] *= pw[n - 1 - j]; }
+    __syncthreads();
+    float* Uc = U + ((size_t)blockIdx.x * p.H + h) * d * dv;
+    tile_product(skT, C, sv, vP, d, dv, nP, [&](int r, int cc, float a) { Uc[r * dv + cc] = a; });
+}
+
+__global__ void __launch_bounds__(NT)
+retention_scan_kernel(RetParams p, int num_requests, float* __restrict__ U) {
+    pdl_launch_dependents();
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int e = blockIdx.x * NT + threadIdx.x;
+    const int t0 = p.q_start[b], len = p.q_start[b + 1] - t0;
+    const int slot = p.slots[b];
+    const float decay = p.decay[h];
+    int first_chunk = 0;                                               // chunks of the requests ahead of b
+    for (int r = 0; r < b; ++r) {
+        const int l = p.q_start[r + 1] - p.q_start[r];
+        if (l > 0) first_chunk += (p.pos_start[r] + l - 1) / C - p.pos_start[r] / C + 1;
+    }
+    pdl_wait();
+    if (len <= 0 || slot < 0 || slot >= p.num_slots || e >= p.d * p.dv) return;
+    const int pos0 = p.pos_start[b];
+    const int count = (pos0 + len - 1) / C - pos0 / C + 1;
+    float* gs = p.state + ((size_t)slot * p.H + h) * p.d * p.dv + e;
+    float S = *gs;
+    for (int c = 0; c < count; ++c) {
+        const int lo = max(pos0, (pos0 / C + c) * C), hi = min(pos0 + len, (pos0 / C + c + 1) * C);
+        float* u = U + ((size_t)(first_chunk + c) * p.H + h) * p.d * p.dv + e;
+        const float add = *u;
+        *u = S;
+        float g = 1.f;
+        for (int i = 0; i < hi - lo; ++i) g *= decay;                  // the same product as the other kernels' table
+        S = fmaf(g, S, add);
+    }
+    *gs = S;
+}
 
 template <typename TO>
 __global__ void __launch_bounds__(NT)
-retention_chunk_kernel(RetParams p) {
-    extern __shared__ float sm[];
-    __shared__ float pw[C + 1];         // decay^0 .. decay^C
-    __shared__ float red[32];
+retention_finish_kernel(RetParams p, int num_requests, const float* __restrict__ acc, const float* __restrict__ U) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float pw[C + 1];
     pdl_launch_dependents();
-    const int h = blockIdx.x, b = blockIdx.y;
-    const int d = p.d, dv = p.dv, dq = d + 1;
-    float* S = sm;                      // [d][dv]
-    float* sq = S + d * dv;             // [C][d+1]
-    float* sk = sq + C * dq;            // [C][d+1]
-    float* sv = sk + C * dq;            // [C][dv]
-    float* A = sv + C * dv;             // [C][C+1]
-    float* so = A + C * (C + 1);        // [C][dv]
-    const int t0 = p.q_start[b], t1 = p.q_start[b + 1];
-    const int pos0 = p.pos_start[b];
-    const int slot = p.slots[b];
-    const float decay = p.decay[h];
-    if (threadIdx.x == 0) { float x = 1.f; for (int i = 0; i <= C; ++i) { pw[i] = x; x *= decay; } }
+    const int h = blockIdx.y, d = p.d, dv = p.dv, dP = pad4(d), vP = pad4(dv);
+    float* sq = sm;                      // [C][dP]
+    float* sS = sq + C * dP;             // [dP][vP]
+    float* so = sS + dP * vP;            // [C][vP]
+    ChunkRef c;
+    const bool have = find_chunk(p, num_requests, blockIdx.x, c);
+    fill_powers(pw, p.decay[h]);
     pdl_wait();
-    if (t1 <= t0 || slot < 0 || slot >= p.num_slots) return;
-    float* gs = p.state + ((size_t)slot * p.H + h) * d * dv;
-    for (int e = threadIdx.x; e < d * dv; e += NT) S[e] = gs[e];
-    int t = t0;
-    while (t < t1) {
-        const int pos = pos0 + (t - t0);
-        const int n = min(t1 - t, C - pos % C);                 // tokens of this chunk (ends at a multiple of C)
-        __syncthreads();
-        for (int e = threadIdx.x; e < n * d; e += NT) {
-            const int i = e / d, c = e % d;
-            sq[i * dq + c] = p.q[(size_t)(t + i) * p.H * d + (size_t)h * d + c];
-            sk[i * dq + c] = p.k[(size_t)(t + i) * p.H * d + (size_t)h * d + c];
-        }
-        for (int e = threadIdx.x; e < n * dv; e += NT) {
-            const int i = e / dv, c = e % dv;
-            sv[e] = p.vg[(size_t)(t + i) * p.ld + p.v_off + h * dv + c];
-        }
-        __syncthreads();
-        // A[i][j] = decay^(i-j) (q_i . k_j) for j <= i
-        for (int e = threadIdx.x; e < n * n; e += NT) {
-            const int i = e / n, jj = e % n;
-            float a = 0.f;
-            if (jj <= i) {
-                for (int c = 0; c < d; ++c) a = fmaf(sq[i * dq + c], sk[jj * dq + c], a);
-                a *= pw[i - jj];
-            }
-            A[i * (C + 1) + jj] = a;
-        }
-        __syncthreads();
-        // o[i][c] = decay^(i+1) sum_r q_i[r] S[r][c] + sum_(j<=i) A[i][j] v_j[c]
-        for (int e = threadIdx.x; e < n * dv; e += NT) {
-            const int i = e / dv, c = e % dv;
-            float a = 0.f;
-            for (int r = 0; r < d; ++r) a = fmaf(sq[i * dq + r], S[r * dv + c], a);
-            a *= pw[i + 1];
-            for (int jj = 0; jj <= i; ++jj) a = fmaf(A[i * (C + 1) + jj], sv[jj * dv + c], a);
-            so[e] = a;
-        }
-        __syncthreads();
-        // S = decay^n S + sum_j decay^(n-1-j) k_j v_j^T
-        for (int e = threadIdx.x; e < d * dv; e += NT) {
-            const int r = e / dv, c = e % dv;
-            float a = S[e] * pw[n];
-            for (int jj = 0; jj < n; ++jj) a = fmaf(sk[jj * dq + r] * pw[n - 1 - jj], sv[jj * dv + c], a);
-            S[e] = a;
-        }
-        // the rows' norms and gates: a warp per token
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        for (int i = warp; i < n; i += NT / 32) {
-            float ss = 0.f;
-            for (int c = lane; c < dv; c += 32) ss = fmaf(so[i * dv + c], so[i * dv + c], ss);
-            ss = warp_sum(ss);
-            const float rs = rsqrtf(ss / (float)dv + p.eps);
-            for (int c = lane; c < dv; c += 32) {
-                const float g = p.vg[(size_t)(t + i) * p.ld + p.g_off + h * dv + c];
-                ((TO*)p.out)[(size_t)(t + i) * p.H * dv + (size_t)h * dv + c] =
-                    from_f32<TO>((so[i * dv + c] * rs) * (g / (1.0f + expf(-g))));
-            }
-        }
-        t += n;
-    }
+    if (!have) return;
+    const int n = c.n;
+    for (int e = threadIdx.x; e < C * dP + dP * vP; e += NT) sm[e] = 0.f;
     __syncthreads();
-    for (int e = threadIdx.x; e < d * dv; e += NT) gs[e] = S[e];
-    (void)red;
+    for (int e = threadIdx.x; e < n * d; e += NT) {
+        const int i = e / d, r = e % d;
+        sq[i * dP + r] = p.q[(size_t)(c.t + i) * p.H * d + (size_t)h * d + r];
+    }
+    const float* Sc = U + ((size_t)blockIdx.x * p.H + h) * d * dv;
+    for (int e = threadIdx.x; e < d * dv; e += NT) sS[(e / dv) * vP + e % dv] = Sc[e];
+    __syncthreads();
+    tile_product(sq, dP, sS, vP, n, dv, dP, [&](int i, int r, float a) {
+        so[i * vP + r] = fmaf(pw[i + 1], a, acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + r]);
+    });
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = warp; i < n; i += NT / 32) {                         // the rows' norms and gates: a warp per token
+        float ss = 0.f;
+        for (int r = lane; r < dv; r += 32) ss = fmaf(so[i * vP + r], so[i * vP + r], ss);
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)dv + p.eps);
+        for (int r = lane; r < dv; r += 32) {
+            const float g = p.vg[(size_t)(c.t + i) * p.ld + p.g_off + h * dv + r];
+            if (p.clear) p.vg[(size_t)(c.t + i) * p.ld + p.g_off + h * dv + r] = 0.f;
+            ((TO*)p.out)[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + r] =
+                from_f32<TO>((so[i * vP + r] * rs) * (g / (1.0f + expf(-g))));
+        }
+    }
 }
 
 }  // namespace
 
-// chunked != 0: the chunk-by-chunk kernel (portions of prompts); else token by token (decoded tokens).
+// Floats of workspace the chunked form needs for a step of ``num_tokens`` tokens in ``num_requests`` requests.
+TFF_API long long tff_retention_workspace(int num_tokens, int num_requests, int H, int d, int dv) {
+    const long long chunks = num_tokens / C + 2ll * num_requests;
+    return (long long)num_tokens * H * dv + chunks * H * d * dv;
+}
+
+// clear_vg != 0: the v and g columns of ``vg`` are set to zero once read.
+// chunked != 0: chunk by chunk (portions of prompts; ``workspace`` of tff_retention_workspace floats, ``num_tokens``
+// the step's tokens); else token by token (decoded tokens).  TFF_ERR_UNSUPPORTED when a head does not fit the
+// shared memory of the form asked for.
 TFF_API int tff_retention(
-    const float* q, const float* k, const float* vg, int ld, int v_off, int g_off,
+    const float* q, const float* k, float* vg, int clear_vg, int ld, int v_off, int g_off,
     float* state, int num_slots, const int* q_start, const int* pos_start, const int* slots, const float* decay,
-    void* out, int out_is_bf16, int num_requests, int H, int d, int dv, float eps, int chunked, cudaStream_t stream) {
+    void* out, int out_is_bf16, int num_requests, int H, int d, int dv, float eps, int chunked,
+    float* workspace, int num_tokens, cudaStream_t stream) {
     if (num_requests <= 0) return TFF_OK;
     if (!q || !k || !vg || !state || !q_start || !pos_start || !slots || !decay || !out || H <= 0 || d <= 0 || dv <= 0)
         return TFF_ERR_BAD_ARGUMENT;
-    if (dv > NT || num_requests > 65535) return TFF_ERR_UNSUPPORTED;
+    if (num_requests > 65535 || H > 65535) return TFF_ERR_UNSUPPORTED;
     RetParams p;
-    p.q = q; p.k = k; p.vg = vg; p.ld = ld; p.v_off = v_off; p.g_off = g_off;
+    p.q = q; p.k = k; p.vg = vg; p.clear = clear_vg; p.ld = ld; p.v_off = v_off; p.g_off = g_off;
     p.state = state; p.num_slots = num_slots; p.q_start = q_start; p.pos_start = pos_start; p.slots = slots;
     p.decay = decay; p.out = out; p.H = H; p.d = d; p.dv = dv; p.eps = eps;
-    size_t smem;
-    if (chunked) smem = sizeof(float) * ((size_t)d * dv + 2 * (size_t)C * (d + 1) + 2 * (size_t)C * dv + C * (C + 1));
-    else smem = sizeof(float) * ((size_t)d * dv + 2 * d + dv + NT + 32);
-    if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
-#define TFF_RET(KERN)                                                                                              \
-    do {                                                                                                           \
-        auto kern = KERN;                                                                                          \
-        static bool configured = false;                                                                            \
-        if (!configured) {                                                                                         \
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) \
-                return TFF_ERR_LAUNCH;                                                                             \
-            configured = true;                                                                                     \
-        }                                                                                                          \
-        return tff_launch_pdl(kern, dim3(H, num_requests), dim3(NT), smem, stream, p);                             \
-    } while (0)
+    constexpr size_t MOST = 224 * 1024;        // dynamic shared memory a CTA may ask for here (the kernels have a little static on top)
     if (chunked) {
-        if (out_is_bf16) TFF_RET(retention_chunk_kernel<bf16>);
-        TFF_RET(retention_chunk_kernel<float>);
+        if (!workspace || num_tokens <= 0) return TFF_ERR_BAD_ARGUMENT;
+        const int dP = pad4(d), vP = pad4(dv);
+        const size_t smem1 = sizeof(float) * ((size_t)C * dP + (size_t)dP * C + (size_t)C * vP + (size_t)C * C);
+        const size_t smem3 = sizeof(float) * ((size_t)C * dP + (size_t)dP * vP + (size_t)C * vP);
+        if (smem1 > MOST || smem3 > MOST) return TFF_ERR_UNSUPPORTED;
+        const int chunks = num_tokens / C + 2 * num_requests;
+        float* acc = workspace;
+        float* U = workspace + (size_t)num_tokens * H * dv;
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(retention_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess ||
+                cudaFuncSetAttribute(retention_finish_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess ||
+                cudaFuncSetAttribute(retention_finish_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess)
+                return TFF_ERR_LAUNCH;
+            configured = true;
+        }
+        int st = tff_launch_pdl(retention_local_kernel, dim3(chunks, H), dim3(NT), smem1, stream, p, num_requests, acc, U);
+        if (st != TFF_OK) return st;
+        st = tff_launch_pdl(retention_scan_kernel, dim3((d * dv + NT - 1) / NT, H, num_requests), dim3(NT), (size_t)0, stream,
+                            p, num_requests, U);
+        if (st != TFF_OK) return st;
+        if (out_is_bf16)
+            return tff_launch_pdl(retention_finish_kernel<bf16>, dim3(chunks, H), dim3(NT), smem3, stream, p, num_requests,
+                                  (const float*)acc, (const float*)U);
+        return tff_launch_pdl(retention_finish_kernel<float>, dim3(chunks, H), dim3(NT), smem3, stream, p, num_requests,
+                              (const float*)acc, (const float*)U);
     }
-    if (out_is_bf16) TFF_RET(retention_step_kernel<bf16>);
-    TFF_RET(retention_step_kernel<float>);
-#undef TFF_RET
+    if (dv > NT) return TFF_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * ((size_t)d * dv + 2 * d + dv + NT + 32);
+    if (smem > MOST) return TFF_ERR_UNSUPPORTED;
+    {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(retention_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess ||
+                cudaFuncSetAttribute(retention_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess)
+                return TFF_ERR_LAUNCH;
+            configured = true;
+        }
+    }
+    if (out_is_bf16) return tff_launch_pdl(retention_step_kernel<bf16>, dim3(H, num_requests), dim3(NT), smem, stream, p);
+    return tff_launch_pdl(retention_step_kernel<float>, dim3(H, num_requests), dim3(NT), smem, stream, p);
 }

@@ -402,48 +402,46 @@ class CudaKernels:
     def gated_mlp(self, h, w_gate_up, w_down, residual, inter: int, activation: str = "silu", out=None) -> None:
         """residual += down(act(gate(h)) * up(h)); ``h`` the activation rows or a DeferredNorm of them.  With
         ``residual`` None the result goes to ``out`` (float32 [T, hidden]) instead.  ``activation``: "silu" or
-        "gelu_tanh"; the kernels with the activation in a product's epilogue know silu only, another activation
-        runs the product and the activation kernel.
+        "gelu_tanh" (the tanh form of gelu).
         A decode step of at most FOLD_MAX_M tokens in bfloat16 whose norm has been deferred runs two kernels:
-        norm, gate/up product and SwiGLU as one (clusters of CTAs share a tile's K range), then the down
+        norm, gate/up product and activation as one (clusters of CTAs share a tile's K range), then the down
         product.  Everything else runs the products and kernels one by one."""
         T = h.shape[0]
-        if residual is None or activation != "silu":
-            if isinstance(h, DeferredNorm):
-                h = h.materialize()
-            act = torch.empty((T, inter), dtype=h.dtype, device=h.device)
-            self.gemm_gated_act(h, w_gate_up, act, activation)
+        code = self.ACTIVATION_CODES[activation]
+        target = residual if residual is not None else out
+
+        def down(act):
             if residual is None:
                 self.gemm(act, w_down, out)
             else:
                 self.gemm(act, w_down, residual, residual=residual)
-            return
+
         if isinstance(h, DeferredNorm):
             if (self.gate_up_block(inter) == 64 and self._foldable_weight(w_gate_up)
-                    and residual.is_cuda and residual.dtype == torch.float32):
-                act = torch.empty((T, inter), dtype=torch.bfloat16, device=residual.device)
+                    and target.is_cuda and target.dtype == torch.float32):
+                act = torch.empty((T, inter), dtype=torch.bfloat16, device=target.device)
                 self._need_cuda(h.x, h.weight, w_gate_up, act)
                 assert tuple(w_gate_up.shape) == (2 * inter, h.x.shape[1])
-                self._check(self.lib.tff_gemm_tc_cluster_swiglu(
+                self._check(self.lib.tff_gemm_tc_cluster_gated(
                     _ptr(h.x), _ptr(h.weight), _c_float(h.eps), _ptr(w_gate_up), _c_int(T), _c_int(h.x.shape[1]),
-                    _ptr(act), _c_int(inter), self._stream()), "gemm_tc_cluster_swiglu")
+                    _ptr(act), _c_int(inter), _c_int(code), self._stream()), "gemm_tc_cluster_gated")
                 self.launches += 1
-                self.gemm(act, w_down, residual, residual=residual)
+                down(act)
                 return
             h = h.materialize()
         act = torch.empty((T, inter), dtype=h.dtype, device=h.device)
         if (self.FOLD_DECODE and T <= self.CLUSTER_MAX_M and h.dtype == torch.bfloat16 and h.is_cuda and h.is_contiguous()
                 and self.gate_up_block(inter) == 64 and self._foldable_weight(w_gate_up) and h.data_ptr() % 16 == 0):
-            # the product with SwiGLU in the first CTA of each cluster: no float32 accumulators, no SwiGLU kernel
+            # the product with the activation in the first CTA of each cluster: no float32 accumulators, no activation kernel
             self._need_cuda(h, w_gate_up, act)
             assert tuple(w_gate_up.shape) == (2 * inter, h.shape[1])
-            self._check(self.lib.tff_gemm_tc_cluster_swiglu_bf16(_ptr(h), _ptr(w_gate_up), _c_int(T), _c_int(h.shape[1]),
-                                                                 _ptr(act), _c_int(inter), self._stream()),
-                        "gemm_tc_cluster_swiglu_bf16")
+            self._check(self.lib.tff_gemm_tc_cluster_gated_bf16(_ptr(h), _ptr(w_gate_up), _c_int(T), _c_int(h.shape[1]),
+                                                                _ptr(act), _c_int(inter), _c_int(code), self._stream()),
+                        "gemm_tc_cluster_gated_bf16")
             self.launches += 1
         else:
-            self.gemm_swiglu(h, w_gate_up, act)
-        self.gemm(act, w_down, residual, residual=residual)
+            self.gemm_gated_act(h, w_gate_up, act, activation)
+        down(act)
 
     def swiglu(self, gate_up, out, block: int = 0) -> None:
         """out[t, i] = silu(gate[t, i]) * up[t, i]; gate_up float32 or of out's type, [gate | up] (block = 0) or
@@ -470,21 +468,6 @@ class CudaKernels:
         if clear:
             self._acc_zero[gate_up.data_ptr()] = True
         self.launches += 1
-
-    def gemm_gated_act(self, a, w_gate_up, out, activation: str) -> None:
-        """out[T, I] = act(a @ Wg^T) * (a @ Wu^T), w_gate_up being merge_gate_up(Wg, Wu)."""
-        if activation == "silu":
-            return self.gemm_swiglu(a, w_gate_up, out)
-        T, I = out.shape
-        K = a.shape[1]
-        tc = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0
-              and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
-        if tc and T <= self.SWAP_MAX_M:
-            gu = self.projection_buffer(T, 2 * I, out.device, out.dtype)
-        else:
-            gu = torch.empty((T, 2 * I), dtype=out.dtype, device=out.device)
-        self.gemm(a, w_gate_up, gu)
-        self.gated_act(gu, out, self.gate_up_block(I), activation)
 
     # ------------------------------------------------------- residual of several streams
     def stream_step(self, x, y=None, scale=None, mix=None, out=None, read=None, norm_weight=None, eps: float = 0.0,
@@ -519,11 +502,14 @@ class CudaKernels:
 
     # ------------------------------------------------------- mixers with a rotation computed on the fly
     def qkv_finish(self, proj, q_out, k_out, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
-                   k_scale: float = 1.0, v_mode: int = 0, v_share=None, lam=None, gate_off: int = -1, gate_out=None) -> None:
+                   k_scale: float = 1.0, v_mode: int = 0, v_share=None, lam=None, gate_off: int = -1, gate_out=None,
+                   last_reader: bool = True) -> None:
         """proj [T, ld] = [q (nq*d) | k (nkv*d) | v (nkv*dv) | ...] -> rotated q in ``q_out`` [T, nq*d]; rotated k
         (times ``k_scale``) and v into the tokens' cache slots or, with no cache, k into ``k_out`` (float32);
         ``freq`` = (frequencies, rot_dim, magnitude, interleaved) or None; value mixing and head gates as
-        csrc/qkv_finish.cu describes them."""
+        csrc/qkv_finish.cu describes them.  When ``proj`` is one of the accumulator buffers that are kept at zero
+        between uses, what the kernel consumes is set back to zero; ``last_reader`` says that nothing of the row is
+        left for another kernel (which then clears the rest)."""
         self._need_cuda(proj, q_out, k_out, block_table, v_share, lam, gate_out)
         T, ld = proj.shape
         f, rot, mag, inter = freq if freq is not None else (None, 0, 1.0, False)
@@ -531,14 +517,17 @@ class CudaKernels:
         dc = kv_cache.shape[-1] if kv_cache is not None else 0
         if kv_cache is not None:
             assert tuple(kv_cache.shape[2:5]) == (2, nkv, page_size)
+        clear = 1 if proj.data_ptr() in self._acc_zero else 0
         self._check(self.lib.tff_qkv_finish(
-            _ptr(proj), _c_int(_dt(proj)), _c_int(ld), _ptr(q_out), _c_int(_dt(q_out)), _ptr(k_out),
+            _ptr(proj), _c_int(_dt(proj)), _c_int(clear), _c_int(ld), _ptr(q_out), _c_int(_dt(q_out)), _ptr(k_out),
             _ptr(f), _c_int(rot), _c_float(mag), _c_int(1 if inter else 0), _c_float(k_scale),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
             c_ptr, _c_int(_dt(kv_cache)) if kv_cache is not None else _c_int(0), _c_int(c_layers), _c_int(c_layer),
             _c_int(page_size), _c_int(dc), _c_int(v_mode), _ptr(v_share), _ptr(lam), _c_int(gate_off), _ptr(gate_out),
             _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), self._stream()), "qkv_finish")
+        if clear and last_reader:
+            self._acc_zero[proj.data_ptr()] = True
         self.launches += 1
 
     def attend_gated(self, h, w_in, freq, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv,
@@ -602,18 +591,41 @@ class CudaKernels:
         self.gemm(h, w_in, proj)
         q = torch.empty((T, H * d), dtype=torch.float32, device=h.device)
         k = torch.empty((T, H * d), dtype=torch.float32, device=h.device)
-        self.qkv_finish(proj, q, k, freq, batch, None, None, 0, 0, H, H, d, dv, k_scale)
-        ld, v_off, g_off = proj.shape[1], 2 * H * d, 2 * H * d + H * dv
-        chunked = 0 if batch.max_q_len == 1 else 1
-        args = lambda ch: (_ptr(q), _ptr(k), _ptr(proj), _c_int(ld), _c_int(v_off), _c_int(g_off), _ptr(state),
+        self.qkv_finish(proj, q, k, freq, batch, None, None, 0, 0, H, H, d, dv, k_scale, last_reader=False)
+        self.retention(q, k, proj, 2 * H * d, 2 * H * d + H * dv, state, batch, decay, out, H, d, dv, eps)
+
+    def retention(self, q, k, vg, v_off: int, g_off: int, state, batch, decay, out, H, d, dv, eps: float,
+                  chunked: Optional[bool] = None) -> None:
+        """The recurrence S <- decay S + k v^T, o = S^T q per head over ``state`` [slots, H, d, dv] (float32), then
+        o / rms(o) * silu(g) -> out [T, H*dv].  q, k float32 [T, H*d] (rotated, k scaled); v and g are columns
+        v_off.. and g_off.. of the float32 rows ``vg``.  ``chunked`` None: token by token when every request brings
+        one token, chunk by chunk otherwise (and token by token where a head's state and a chunk do not fit in
+        shared memory)."""
+        self._need_cuda(q, k, vg, state, decay, out)
+        assert q.dtype == k.dtype == vg.dtype == state.dtype == decay.dtype == torch.float32
+        assert tuple(state.shape[1:]) == (H, d, dv) and decay.numel() == H and out.shape[1] == H * dv
+        if chunked is None:
+            chunked = batch.max_q_len > 1
+        T = q.shape[0]
+        ws = None
+        if chunked:
+            self.lib.tff_retention_workspace.restype = ctypes.c_longlong
+            need = int(self.lib.tff_retention_workspace(_c_int(T), _c_int(batch.num_requests), _c_int(H), _c_int(d), _c_int(dv)))
+            ws = torch.empty(need, dtype=torch.float32, device=q.device)
+        clear = 1 if vg.data_ptr() in self._acc_zero else 0
+        args = lambda ch: (_ptr(q), _ptr(k), _ptr(vg), _c_int(clear), _c_int(vg.shape[1]), _c_int(v_off), _c_int(g_off), _ptr(state),
                            _c_int(state.shape[0]), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(batch.slots),
                            _ptr(decay), _ptr(out), _c_int(_dt(out)), _c_int(batch.num_requests), _c_int(H), _c_int(d),
-                           _c_int(dv), _c_float(eps), _c_int(ch), self._stream())
-        status = self.lib.tff_retention(*args(chunked))
+                           _c_int(dv), _c_float(eps), _c_int(ch), _ptr(ws) if ch else _vp(0), _c_int(T), self._stream())
+        status = self.lib.tff_retention(*args(1 if chunked else 0))
+        kernels = 3 if chunked else 1
         if status == -2 and chunked:
-            status = self.lib.tff_retention(*args(0))      # heads too large for the chunked kernel's shared memory
+            status = self.lib.tff_retention(*args(0))      # a head too large for the chunked form's shared memory
+            kernels = 1
         self._check(status, "retention")
-        self.launches += 1
+        if clear:
+            self._acc_zero[vg.data_ptr()] = True
+        self.launches += kernels
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
         """table float32 [max_pos, rot_dim/2, 2] = (cos, sin)(pos * theta^(-2i/rot_dim)).
@@ -885,6 +897,10 @@ class CudaKernels:
 
     def gemm_swiglu(self, a, w_gate_up, out) -> None:
         """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T), w_gate_up being merge_gate_up(Wg, Wu)."""
+        self.gemm_gated_act(a, w_gate_up, out, "silu")
+
+    def gemm_gated_act(self, a, w_gate_up, out, activation: str) -> None:
+        """out[T, I] = act(a @ Wg^T) * (a @ Wu^T), act "silu" or "gelu_tanh"."""
         self._need_cuda(a, w_gate_up, out)
         T, I = out.shape
         K = a.shape[1]
@@ -896,9 +912,9 @@ class CudaKernels:
             # swapped product and the SwiGLU kernel behind it took 45 us at 72 rows of the 8B shape against 39, 78
             # against 59 at 256
             bn = self.prompt_plan(T, 2 * I, K, False)[1]
-            self._check(self.lib.tff_gemm_tc_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
-                                                    _c_int(K), _c_int(bn), self._stream()),
-                        "gemm_tc_swiglu")
+            self._check(self.lib.tff_gemm_tc_gated(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
+                                                   _c_int(K), _c_int(bn), _c_int(self.ACTIVATION_CODES[activation]),
+                                                   self._stream()), "gemm_tc_gated")
             self.launches += 1
             return
         small = tc and T <= self.SWAP_MAX_M
@@ -907,7 +923,8 @@ class CudaKernels:
         else:
             gu = torch.empty((T, 2 * I), dtype=out.dtype, device=out.device)
         self.gemm(a, w_gate_up, gu)
-        self.swiglu(gu, out, block)
+        self.gated_act(gu, out, block, activation)
+
     def argmax(self, logits, out) -> None:
         self._need_cuda(logits, out)
         R, V = logits.shape

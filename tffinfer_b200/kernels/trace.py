@@ -28,7 +28,9 @@ import torch
 
 TRACED = ("embed", "rmsnorm", "gemm", "gemm_simt", "gemm_tc", "zero_f32", "gather_tokens", "swiglu", "gemm_swiglu",
           "qkv_project", "qk_norm_rope_kv_write", "attention", "attention_bf16", "attention_generic", "argmax",
-          "sample", "repetition_penalty", "reset_state_slots", "logit_transform", "rope_table")
+          "sample", "repetition_penalty", "reset_state_slots", "logit_transform", "rope_table", "stream_step",
+          "qkv_finish", "attend_gated", "attention_ext", "retain", "retention", "gated_act", "gemm_gated_act",
+          "gated_mlp")
 
 
 class KernelTrace:
