@@ -336,3 +336,54 @@ def test_greedy_generation_through_the_engine(dtype, name):
                 break
             assert int(logits.argmax()) == o[i], f"token {i} differs"
             seq.append(o[i])
+
+
+# ------------------------------------------------------------------------------ the replay tool and the command line
+def test_trace_replay_tool_on_a_model_folder(tmp_path):
+    """bin/trace_run on a Tipezen folder written by the random-weights mode: a mixed schedule (portions beside single
+    tokens, four live requests, a pool that makes later requests reuse pages and slots) in both number formats."""
+    import numpy as np
+    from test_trace_run_gpu import _replay, _max_tokens
+    from helpers import steps_to_jsonl
+    from tffinfer_b200.weights import write_random_model
+    from tffinfer_b200.weights.safetensors_io import SafetensorsFile
+    cfg = config("a")
+    d = write_random_model(str(tmp_path / "model"), cfg, seed=5)
+    f = SafetensorsFile(str(tmp_path / "model" / "model.safetensors"))
+    sd = {n: f.tensor(n).clone() for n in f.names()}
+    rng = random.Random(9)
+    prompts = [70, 3, 130, 41, 18]
+    reqs = {f"q{i}": [rng.randrange(cfg.vocab_size) for _ in range(n + 10)] for i, n in enumerate(prompts)}
+    want = {r: P.forward(cfg.to_json_dict(), sd, t) for r, t in reqs.items()}
+    steps = trace_mixed(reqs, prompts, max_live=4, page_size=64, pool_tokens=384, chunk=33)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        out.mkdir()
+        assert _replay(d, dtype, _max_tokens(reqs, steps), steps_to_jsonl(reqs, steps), str(out)) == 0
+        got = {r: [None] * len(t) for r, t in reqs.items()}
+        for i, (entries, _) in enumerate(steps):
+            rows = sum(n for _, _, n in entries)
+            arr = torch.from_numpy(np.fromfile(str(out / f"{i}.f32"), dtype="<f4").reshape(rows, cfg.vocab_size))
+            row = 0
+            for r, start, n in entries:
+                for k in range(n):
+                    got[r][start + k] = arr[row]
+                    row += 1
+        for r in reqs:
+            assert first_bad(torch.stack(got[r]), want[r], TOL[dtype]) is None, (dtype, r)
+
+
+def test_command_line_generates(tmp_path):
+    import json
+    import subprocess
+    import sys
+    import os
+    from tffinfer_b200.weights import write_random_model
+    d = write_random_model(str(tmp_path / "model"), config("b"), seed=1)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "tffinfer_b200", d, "--prompt-ids", "1,2,3,4,5", "--prompt-ids", "7,8",
+                        "--n-predict", "12", "--max-live", "2", "--max-cache-tokens", "128", "--json"],
+                       cwd=root, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = json.loads(p.stdout.strip().splitlines()[-1])
+    assert [len(o) for o in out["outputs"]] == [12, 12]

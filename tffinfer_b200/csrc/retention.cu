@@ -33,15 +33,19 @@ struct RetParams {
 };
 
 // ------------------------------------------------------------------ token by token
-template <typename TO>
+// IN_SMEM: the head's state fits shared memory beside the rest (else it is worked on where it lies)
+template <typename TO, bool IN_SMEM>
 __global__ void __launch_bounds__(NT)
 retention_step_kernel(RetParams p) {
+    constexpr bool state_in_smem = IN_SMEM;
     extern __shared__ float sm[];
     pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
     const int d = p.d, dv = p.dv;
-    float* S = sm;                      // [d][dv]
-    float* sq = S + d * dv;             // [d]
+    float* S;
+    if constexpr (IN_SMEM) S = sm;
+    else S = p.state + ((size_t)min(max(p.slots[b], 0), p.num_slots - 1) * p.H + h) * d * dv;
+    float* sq = sm + (state_in_smem ? d * dv : 0);   // [d]
     float* sk = sq + d;                 // [d]
     float* sv = sk + d;                 // [dv]
     float* part = sv + dv;              // [NY][dv]
@@ -55,7 +59,7 @@ retention_step_kernel(RetParams p) {
     pdl_wait();
     if (t1 <= t0 || slot < 0 || slot >= p.num_slots) return;
     float* gs = p.state + ((size_t)slot * p.H + h) * d * dv;
-    for (int e = threadIdx.x; e < d * dv; e += NT) S[e] = gs[e];
+    if (state_in_smem) for (int e = threadIdx.x; e < d * dv; e += NT) S[e] = gs[e];
     for (int t = t0; t < t1; ++t) {
         __syncthreads();
         for (int i = threadIdx.x; i < d; i += NT) {
@@ -90,7 +94,7 @@ retention_step_kernel(RetParams p) {
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < d * dv; e += NT) gs[e] = S[e];
+    if (state_in_smem) for (int e = threadIdx.x; e < d * dv; e += NT) gs[e] = S[e];
 }
 
 // ------------------------------------------------------------------ chunk by chunk
@@ -100,7 +104,8 @@ retention_step_kernel(RetParams p) {
 //   1. local:  A = mask(decay^(i-j) q_i . k_j);  acc = A V  (-> acc [T, H*dv]);  U = sum_j decay^(n-1-j) k_j v_j^T (-> U[chunk])
 //   2. scan:   per (request, head, state element), over the request's chunks in order: U[chunk] <- S (the state the
 //              chunk starts from), S <- decay^n S + U[chunk]; the last S goes back to the request's slot
-//   3. finish: o_i = acc_i + decay^(i+1) S^T q_i, then the head's RMS norm and the gate -> out
+//   3. finish: o_i = acc_i + decay^(i+1) S^T q_i (S in blocks of 64 value columns), then the head's RMS norm and
+//              the gate -> out
 // The products are float32 FMAs on 4 x 4 register tiles out of shared memory (operands zero-padded to multiples of 4).
 constexpr int C = 64;
 
@@ -227,17 +232,32 @@ retention_scan_kernel(RetParams p, int num_requests, float* __restrict__ U) {
     const int count = (pos0 + len - 1) / C - pos0 / C + 1;
     float* gs = p.state + ((size_t)slot * p.H + h) * p.d * p.dv + e;
     float S = *gs;
-    for (int c = 0; c < count; ++c) {
-        const int lo = max(pos0, (pos0 / C + c) * C), hi = min(pos0 + len, (pos0 / C + c + 1) * C);
-        float* u = U + ((size_t)(first_chunk + c) * p.H + h) * p.d * p.dv + e;
-        const float add = *u;
-        *u = S;
-        float g = 1.f;
-        for (int i = 0; i < hi - lo; ++i) g *= decay;                  // the same product as the other kernels' table
-        S = fmaf(g, S, add);
+    const size_t stride = (size_t)p.H * p.d * p.dv;                   // floats between a chunk's U and the next one's
+    float* u0 = U + ((size_t)first_chunk * p.H + h) * p.d * p.dv + e;
+    // eight chunks' U are asked for together, then the state walks through them: the loads of a chunk do not wait
+    // for the chunk before
+    for (int c0 = 0; c0 < count; c0 += 8) {
+        float add[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) add[j] = c0 + j < count ? u0[(size_t)(c0 + j) * stride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j;
+            if (c < count) {
+                const int lo = max(pos0, (pos0 / C + c) * C), hi = min(pos0 + len, (pos0 / C + c + 1) * C);
+                u0[(size_t)c * stride] = S;
+                float g = 1.f;
+                for (int i = 0; i < hi - lo; ++i) g *= decay;          // the same product as the other kernels' table
+                S = fmaf(g, S, add[j]);
+            }
+        }
     }
     *gs = S;
 }
+
+// The value columns are worked on in blocks of NB, so that the CTA holds q, one block of S and the outputs (96 KB
+// at 128 x 128: two CTAs an SM, one loading while the other multiplies).
+constexpr int NB = 64;
 
 template <typename TO>
 __global__ void __launch_bounds__(NT)
@@ -247,26 +267,50 @@ retention_finish_kernel(RetParams p, int num_requests, const float* __restrict__
     pdl_launch_dependents();
     const int h = blockIdx.y, d = p.d, dv = p.dv, dP = pad4(d), vP = pad4(dv);
     float* sq = sm;                      // [C][dP]
-    float* sS = sq + C * dP;             // [dP][vP]
-    float* so = sS + dP * vP;            // [C][vP]
+    float* sS = sq + C * dP;             // [dP][NB]
+    float* so = sS + dP * NB;            // [C][vP]
     ChunkRef c;
     const bool have = find_chunk(p, num_requests, blockIdx.x, c);
     fill_powers(pw, p.decay[h]);
     pdl_wait();
     if (!have) return;
     const int n = c.n;
-    for (int e = threadIdx.x; e < C * dP + dP * vP; e += NT) sm[e] = 0.f;
-    __syncthreads();
-    for (int e = threadIdx.x; e < n * d; e += NT) {
-        const int i = e / d, r = e % d;
-        sq[i * dP + r] = p.q[(size_t)(c.t + i) * p.H * d + (size_t)h * d + r];
-    }
     const float* Sc = U + ((size_t)blockIdx.x * p.H + h) * d * dv;
-    for (int e = threadIdx.x; e < d * dv; e += NT) sS[(e / dv) * vP + e % dv] = Sc[e];
-    __syncthreads();
-    tile_product(sq, dP, sS, vP, n, dv, dP, [&](int i, int r, float a) {
-        so[i * vP + r] = fmaf(pw[i + 1], a, acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + r]);
-    });
+    const float* qg = p.q + (size_t)c.t * p.H * d + (size_t)h * d;
+    // rows of four: 16-byte loads when every row starts on such a boundary
+    const bool vec = (d & 3) == 0 && (dv & 3) == 0 && (((uintptr_t)p.q | (uintptr_t)U) & 15) == 0;
+    if (vec) {
+        const int d4 = d >> 2;
+        for (int e = threadIdx.x; e < pad4(n) * d4; e += NT) {
+            const int i = e / d4, r = e % d4;
+            reinterpret_cast<float4*>(sq + i * dP)[r] =
+                i < n ? reinterpret_cast<const float4*>(qg + (size_t)i * p.H * d)[r] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int e = threadIdx.x; e < C * dP; e += NT) sq[e] = 0.f;
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * d; e += NT) sq[(e / d) * dP + e % d] = qg[(size_t)(e / d) * p.H * d + e % d];
+    }
+    for (int n0 = 0; n0 < dv; n0 += NB) {
+        const int nb = min(NB, dv - n0);
+        __syncthreads();                                              // the block before has been multiplied
+        if (vec) {
+            const int b4 = nb >> 2;
+            for (int e = threadIdx.x; e < d * b4; e += NT) {
+                const int r = e / b4, cc = e % b4;
+                reinterpret_cast<float4*>(sS + r * NB)[cc] = reinterpret_cast<const float4*>(Sc + (size_t)r * dv + n0)[cc];
+            }
+        } else {
+            for (int e = threadIdx.x; e < dP * NB; e += NT) {
+                const int r = e / NB, cc = e % NB;
+                sS[e] = (r < d && cc < nb) ? Sc[(size_t)r * dv + n0 + cc] : 0.f;
+            }
+        }
+        __syncthreads();
+        tile_product(sq, dP, sS, NB, n, nb, dP, [&](int i, int r, float a) {
+            so[i * vP + n0 + r] = fmaf(pw[i + 1], a, acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + n0 + r]);
+        });
+    }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = warp; i < n; i += NT / 32) {                         // the rows' norms and gates: a warp per token
@@ -313,7 +357,7 @@ TFF_API int tff_retention(
         if (!workspace || num_tokens <= 0) return TFF_ERR_BAD_ARGUMENT;
         const int dP = pad4(d), vP = pad4(dv);
         const size_t smem1 = sizeof(float) * ((size_t)C * dP + (size_t)dP * C + (size_t)C * vP + (size_t)C * C);
-        const size_t smem3 = sizeof(float) * ((size_t)C * dP + (size_t)dP * vP + (size_t)C * vP);
+        const size_t smem3 = sizeof(float) * ((size_t)C * dP + (size_t)dP * NB + (size_t)C * vP);
         if (smem1 > MOST || smem3 > MOST) return TFF_ERR_UNSUPPORTED;
         const int chunks = num_tokens / C + 2 * num_requests;
         float* acc = workspace;
@@ -338,17 +382,24 @@ TFF_API int tff_retention(
                               (const float*)acc, (const float*)U);
     }
     if (dv > NT) return TFF_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * ((size_t)d * dv + 2 * d + dv + NT + 32);
+    const size_t rest = sizeof(float) * ((size_t)2 * d + dv + NT + 32);
+    const int in_smem = sizeof(float) * (size_t)d * dv + rest <= MOST ? 1 : 0;
+    const size_t smem = rest + (in_smem ? sizeof(float) * (size_t)d * dv : 0);
     if (smem > MOST) return TFF_ERR_UNSUPPORTED;
     {
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(retention_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess ||
-                cudaFuncSetAttribute(retention_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess)
+            if (cudaFuncSetAttribute(retention_step_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess ||
+                cudaFuncSetAttribute(retention_step_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST) != cudaSuccess)
                 return TFF_ERR_LAUNCH;
             configured = true;
         }
     }
-    if (out_is_bf16) return tff_launch_pdl(retention_step_kernel<bf16>, dim3(H, num_requests), dim3(NT), smem, stream, p);
-    return tff_launch_pdl(retention_step_kernel<float>, dim3(H, num_requests), dim3(NT), smem, stream, p);
+    const dim3 grid(H, num_requests);
+    if (in_smem) {
+        if (out_is_bf16) return tff_launch_pdl(retention_step_kernel<bf16, true>, grid, dim3(NT), smem, stream, p);
+        return tff_launch_pdl(retention_step_kernel<float, true>, grid, dim3(NT), smem, stream, p);
+    }
+    if (out_is_bf16) return tff_launch_pdl(retention_step_kernel<bf16, false>, grid, dim3(NT), smem, stream, p);
+    return tff_launch_pdl(retention_step_kernel<float, false>, grid, dim3(NT), smem, stream, p);
 }

@@ -15,21 +15,36 @@
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MOST_STREAMS = 16;
 
-template <typename TO, int NT>
+// four consecutive outputs in one store
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+// MAX_STREAMS: the register arrays' size, the smallest of 4, 8, 16 that holds S
+template <typename TO, int NT, int MAX_STREAMS>
 __global__ void __launch_bounds__(NT)
 stream_step_kernel(float* __restrict__ x, int S, int W,
                    const float* __restrict__ y, const float* __restrict__ scale,
                    const float* __restrict__ mix, const float* __restrict__ outw,
                    const float* __restrict__ inw, const float* __restrict__ w, float eps,
                    const int* __restrict__ row_index, TO* __restrict__ h, float* __restrict__ total) {
-    extern __shared__ float u_row[];                 // W floats: the combined row, kept between the two passes
+    extern __shared__ __align__(16) float u_row[];   // W floats: the combined row, kept between the two passes
     __shared__ float red[32];
     __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+    static_assert(MAX_STREAMS * MAX_STREAMS <= NT * 4, "the coefficients are loaded in a few passes");
     pdl_launch_dependents();
     // the coefficients and the row index are older than the kernel ahead
-    if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S == threadIdx.x % S) ? 1.f : 0.f);
+    for (int e = threadIdx.x; e < S * S; e += NT) c_mix[e] = mix ? mix[e] : ((e / S == e % S) ? 1.f : 0.f);
     if (threadIdx.x < S) {
         c_out[threadIdx.x] = outw ? outw[threadIdx.x] : 1.f;
         c_in[threadIdx.x] = inw ? inw[threadIdx.x] : 1.f;
@@ -41,6 +56,73 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
     float* xr = x + (size_t)row * S * W;
     const float* yr = y ? y + (size_t)row * W : nullptr;
     float ss = 0.f;
+    // four columns a thread at a time (16-byte accesses) when the rows allow it; which path runs depends on W and
+    // the buffers' alignment alone, so a row's sums are always added in the same order
+    const bool vec = MAX_STREAMS <= 8 && (W & 3) == 0 &&
+                     (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)total) & 15) == 0;
+    if (vec) {
+        const int W4 = W >> 2;
+        for (int i = threadIdx.x; i < W4; i += NT) {
+            float4 v[MAX_STREAMS];
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+                v[s] = s < S ? reinterpret_cast<const float4*>(xr + (size_t)s * W)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (yr) {
+                float4 ys = reinterpret_cast<const float4*>(yr)[i];
+                if (scale) {
+                    const float4 g = reinterpret_cast<const float4*>(scale)[i];
+                    ys.x *= g.x; ys.y *= g.y; ys.z *= g.z; ys.w *= g.w;
+                }
+                float4 n[MAX_STREAMS];
+#pragma unroll
+                for (int t = 0; t < MAX_STREAMS; ++t) {
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; ++s)
+                        if (s < S && t < S) {
+                            const float m = c_mix[s * S + t];
+                            a.x = fmaf(m, v[s].x, a.x); a.y = fmaf(m, v[s].y, a.y);
+                            a.z = fmaf(m, v[s].z, a.z); a.w = fmaf(m, v[s].w, a.w);
+                        }
+                    const float o = t < S ? c_out[t] : 0.f;
+                    n[t] = make_float4(fmaf(o, ys.x, a.x), fmaf(o, ys.y, a.y), fmaf(o, ys.z, a.z), fmaf(o, ys.w, a.w));
+                }
+#pragma unroll
+                for (int t = 0; t < MAX_STREAMS; ++t)
+                    if (t < S) { v[t] = n[t]; reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = n[t]; }
+            }
+            if (h || total) {
+                float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < S) {
+                        const float m = c_in[s];
+                        u.x = fmaf(m, v[s].x, u.x); u.y = fmaf(m, v[s].y, u.y);
+                        u.z = fmaf(m, v[s].z, u.z); u.w = fmaf(m, v[s].w, u.w);
+                    }
+                reinterpret_cast<float4*>(u_row)[i] = u;
+                ss = fmaf(u.x, u.x, ss); ss = fmaf(u.y, u.y, ss); ss = fmaf(u.z, u.z, ss); ss = fmaf(u.w, u.w, ss);
+                if (total) reinterpret_cast<float4*>(total + (size_t)r * W)[i] = u;
+            }
+        }
+        if (!h) return;
+        ss = block_sum<NT>(ss, red);
+        const float rs = rsqrtf(ss / (float)W + eps);
+        TO* o = h + (size_t)r * W;
+        const bool wvec = (((uintptr_t)w) & 15) == 0 && (((uintptr_t)o) & (sizeof(TO) == 2 ? 7 : 15)) == 0;
+        for (int i = threadIdx.x; i < W4; i += NT) {  // a thread reads back what it wrote itself
+            const float4 u = reinterpret_cast<const float4*>(u_row)[i];
+            float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (w) g = wvec ? reinterpret_cast<const float4*>(w)[i] : make_float4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            if (wvec) {
+                store4<TO>(o + 4 * i, (u.x * rs) * g.x, (u.y * rs) * g.y, (u.z * rs) * g.z, (u.w * rs) * g.w);
+            } else {
+                o[4 * i] = from_f32<TO>((u.x * rs) * g.x); o[4 * i + 1] = from_f32<TO>((u.y * rs) * g.y);
+                o[4 * i + 2] = from_f32<TO>((u.z * rs) * g.z); o[4 * i + 3] = from_f32<TO>((u.w * rs) * g.w);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < W; i += NT) {
         float v[MAX_STREAMS];
 #pragma unroll
@@ -103,12 +185,18 @@ TFF_API int tff_stream_step(float* x, int S, int W, const float* y, const float*
                             void* h, int h_is_bf16, float* total, int rows, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (!x || S <= 0 || W <= 0) return TFF_ERR_BAD_ARGUMENT;
-    if (S > MAX_STREAMS) return TFF_ERR_UNSUPPORTED;
+    if (S > MOST_STREAMS) return TFF_ERR_UNSUPPORTED;
     const size_t smem = (size_t)W * sizeof(float);
     if (smem > 96 * 1024) return TFF_ERR_UNSUPPORTED;
 #define TFF_STREAM_LAUNCH(TO, NT)                                                                              \
     do {                                                                                                       \
-        auto kern = stream_step_kernel<TO, NT>;                                                                \
+        if (S <= 4) TFF_STREAM_LAUNCH_S(TO, NT, 4);                                                            \
+        if (S <= 8) TFF_STREAM_LAUNCH_S(TO, NT, 8);                                                            \
+        TFF_STREAM_LAUNCH_S(TO, NT, 16);                                                                       \
+    } while (0)
+#define TFF_STREAM_LAUNCH_S(TO, NT, MS)                                                                        \
+    do {                                                                                                       \
+        auto kern = stream_step_kernel<TO, NT, MS>;                                                            \
         if (smem > 48 * 1024) {                                                                                \
             static bool configured = false;                                                                    \
             if (!configured) {                                                                                 \
@@ -127,6 +215,7 @@ TFF_API int tff_stream_step(float* x, int S, int W, const float* y, const float*
     if (h_is_bf16) TFF_STREAM_LAUNCH(bf16, 64);
     TFF_STREAM_LAUNCH(float, 64);
 #undef TFF_STREAM_LAUNCH
+#undef TFF_STREAM_LAUNCH_S
 }
 
 TFF_API int tff_embed_streams(const int* tokens, const void* table, int table_is_bf16, float* out, int num_tokens,
