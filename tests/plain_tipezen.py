@@ -53,7 +53,7 @@ def rotate(x: torch.Tensor, positions: torch.Tensor, rot: Optional[dict], interl
         return x
     dims = int(rot["dims"])
     f, mag = rotary_frequencies(rot)
-    ang = positions.to(D)[:, None] * f[None, :]                 # [T, dims/2]
+    ang = positions.to(x.dtype)[:, None] * f.to(x.dtype)[None, :]          # [T, dims/2]
     c, s = (torch.cos(ang) * mag)[:, None, :], (torch.sin(ang) * mag)[:, None, :]
     out = x.clone()
     if interleaved:
@@ -73,7 +73,7 @@ def windowed_sink_attention(q, k, v, scale: float, softcap: float, window: int):
     > 0; the weights are exp(s_j) / (1 + sum_j exp(s_j))."""
     T, H, _ = q.shape
     G = k.shape[1]
-    out = torch.zeros(T, H, v.shape[-1], dtype=D)
+    out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
     for h in range(H):
         g = h // (H // G)
         for i in range(T):
@@ -86,9 +86,14 @@ def windowed_sink_attention(q, k, v, scale: float, softcap: float, window: int):
     return out
 
 
-def attention_mixer(h, positions, w: Dict[str, torch.Tensor], p: str, m: dict, v_first: Optional[torch.Tensor]):
+def _same(x):
+    return x
+
+
+def attention_mixer(h, positions, w: Dict[str, torch.Tensor], p: str, m: dict, v_first: Optional[torch.Tensor], r=_same):
     """The attention mixer on its input rows h [T, width].  Returns (output [T, width], the values this layer
-    would hand on as v_first [T, G, dv])."""
+    would hand on as v_first [T, G, dv]).  ``r`` is applied to what a 16-bit engine stores in 16 bits (queries,
+    cached keys and values, the heads' outputs): the identity here, a rounding where conditioning is looked at."""
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
     q = (h @ w[p + ".q"].t()).view(T, H, d)
@@ -101,9 +106,9 @@ def attention_mixer(h, positions, w: Dict[str, torch.Tensor], p: str, m: dict, v
         lam = w[p + ".vmix"]
         v = (1.0 - lam) * v + lam * v_first
     window = int(m["mask"]["size"]) if m.get("mask") else 0
-    o = windowed_sink_attention(q, k, v, float(m["scale"]), float(m.get("softcap") or 0.0), window)
+    o = windowed_sink_attention(r(q), r(k), r(v), float(m["scale"]), float(m.get("softcap") or 0.0), window)
     gate = torch.sigmoid(h @ w[p + ".g"].t())                   # [T, H]
-    o = o * gate[:, :, None]
+    o = r(o * gate[:, :, None])
     return o.reshape(T, H * dv) @ w[p + ".o"].t(), v_own
 
 
@@ -111,16 +116,16 @@ def retention_recurrence(q, k, v, decay: List[float]):
     """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, token by token; q, k [T, H, d], v [T, H, dv]."""
     T, H, d = q.shape
     dv = v.shape[-1]
-    out = torch.zeros(T, H, dv, dtype=D)
+    out = torch.zeros(T, H, dv, dtype=q.dtype)
     for hh in range(H):
-        S = torch.zeros(d, dv, dtype=D)
+        S = torch.zeros(d, dv, dtype=q.dtype)
         for t in range(T):
             S = decay[hh] * S + torch.outer(k[t, hh], v[t, hh])
             out[t, hh] = S.t() @ q[t, hh]
     return out
 
 
-def retention_mixer(h, positions, w, p: str, m: dict, eps: float):
+def retention_mixer(h, positions, w, p: str, m: dict, eps: float, r=_same):
     H, d, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
     q = (h @ w[p + ".q"].t()).view(T, H, d)
@@ -131,11 +136,11 @@ def retention_mixer(h, positions, w, p: str, m: dict, eps: float):
     o = rms(retention_recurrence(q, k, v, [float(x) for x in m["decay"]]), eps)
     g = h @ w[p + ".g"].t()
     g = g / (1.0 + torch.exp(-g))
-    return (o.reshape(T, H * dv) * g) @ w[p + ".o"].t()
+    return r(o.reshape(T, H * dv) * g) @ w[p + ".o"].t()
 
 
-def dense_ff(h, w, p: str):
-    return (gelu_tanh(h @ w[p + ".gate"].t()) * (h @ w[p + ".up"].t())) @ w[p + ".down"].t()
+def dense_ff(h, w, p: str, r=_same):
+    return r(gelu_tanh(h @ w[p + ".gate"].t()) * (h @ w[p + ".up"].t())) @ w[p + ".down"].t()
 
 
 def hyper_read(streams: torch.Tensor, w_in: torch.Tensor) -> torch.Tensor:
@@ -148,9 +153,14 @@ def hyper_write(streams, y, w_mix, w_out):
     return torch.einsum("st,sxw->txw", w_mix, streams) + w_out[:, None, None] * y[None]
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, return_layers: bool = False):
-    """Logits [T, vocab] of one sequence (and, if asked, the sum of the streams after every layer)."""
-    w = {n: t.to(D) for n, t in w.items()}
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, return_layers: bool = False, dtype=D,
+            round_inputs: bool = False):
+    """Logits [T, vocab] of one sequence (and, if asked, the sum of the streams after every layer).  ``dtype``
+    float32 runs everything in 32 bits; ``round_inputs`` rounds every input of a matrix product and the attention's
+    queries, keys and values to bfloat16 and nothing else: the two show how far rounding alone moves a position's
+    logits (the conditioning of a set of weights at that position)."""
+    r = (lambda t: t.to(torch.bfloat16).to(dtype)) if round_inputs else _same
+    w = {n: t.to(dtype) for n, t in w.items()}
     eps = float(cfg["norm"]["eps"])
     S = int(cfg.get("streams") or 0)
     T = len(tokens)
@@ -166,20 +176,21 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, return_layers: bool =
                 continue
             u = hyper_read(streams, w[f"{p}.hc{q}.in"]) if S else streams[0]
             hn = rms(u, eps) * w[f"{p}.norm{q}"]
+            hn = r(hn)
             if q == 2:
-                y = dense_ff(hn, w, p + ".mlp")
+                y = dense_ff(hn, w, p + ".mlp", r)
             elif layer["type"] == "attention":
                 m = layer["mixer"]
-                y, v_own = attention_mixer(hn, pos, w, p + ".mix", m, v_first if m.get("v_mix") else None)
+                y, v_own = attention_mixer(hn, pos, w, p + ".mix", m, v_first if m.get("v_mix") else None, r)
                 if m.get("v_mix") and v_first is None:
                     v_first = v_own
             elif layer["type"] == "retention":
-                y = retention_mixer(hn, pos, w, p + ".mix", layer["mixer"], eps)
+                y = retention_mixer(hn, pos, w, p + ".mix", layer["mixer"], eps, r)
             else:
                 raise ValueError(layer["type"])
             y = y * w[f"{p}.ls{q}"]
             streams = hyper_write(streams, y, w[f"{p}.hc{q}.mix"], w[f"{p}.hc{q}.out"]) if S else streams + y[None]
         after.append(streams.sum(0))
     x = streams.sum(0)
-    logits = (rms(x, eps) * w["final.norm"]) @ w["head"].t()
+    logits = r(rms(x, eps) * w["final.norm"]) @ w["head"].t()
     return (logits, torch.stack(after)) if return_layers else logits

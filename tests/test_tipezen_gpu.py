@@ -387,3 +387,67 @@ def test_command_line_generates(tmp_path):
     assert p.returncode == 0, p.stderr[-2000:]
     out = json.loads(p.stdout.strip().splitlines()[-1])
     assert [len(o) for o in out["outputs"]] == [12, 12]
+
+
+# ------------------------------------------------------------------------------ configurations drawn at random
+def draw(seed: int):
+    """Layer orders, sizes and constants drawn at random: which kernels run (tensor-core or FMA products, the head-64/128
+    attention kernels or the general one, the chunked retention or the token-by-token one) follows from the sizes."""
+    rng = random.Random(seed)
+    W = rng.choice([64, 96, 128, 192, 256]) if rng.random() < 0.75 else rng.choice([36, 100, 150])
+    S = rng.choice([0, 1, 2, 4, 4, 6, 9])
+    n_layers = rng.choice([2, 3, 4, 6])
+    a_heads = rng.choice([1, 2, 4, 8])
+    a_kv = rng.choice([h for h in (1, 2, 4, 8) if a_heads % h == 0])
+    a_dim = rng.choice([16, 32, 64, 64, 128, 48])
+    a_vdim = a_dim if rng.random() < 0.6 else rng.choice([16, 32, 64, 96])
+    rot_a = RotaryConfig(rng.choice([1e4, 5e5]), rng.choice([d for d in (8, 16, 32, 64, 128) if d <= a_dim]),
+                         rng.choice([None, (rng.choice([2.0, 8.0, 32.0]), rng.choice([64.0, 2048.0, 4096.0]),
+                                            rng.choice([16.0, 32.0]), rng.choice([1.0, 2.0]))]))
+    window = rng.choice([5, 16, 40, 64, 100])
+    softcap = rng.choice([0.0, 10.0, 30.0, 50.0])
+    scale = rng.choice([a_dim ** -0.5, 0.125, 0.2])
+    r_heads = rng.choice([1, 2, 3, 4])
+    r_dim = rng.choice([16, 32, 64, 128, 24])
+    r_vdim = rng.choice([16, 32, 64, 128, 40])
+    rot_r = rng.choice([None, RotaryConfig(rng.choice([1e4, 1e6]), rng.choice([d for d in (8, 16, 24, 32, 64, 128) if d <= r_dim]))])
+    layers = []
+    for i in range(n_layers):
+        ff = rng.choice([0, 64, 128, 192, 100])
+        if rng.random() < 0.5:
+            layers.append(att(a_heads, a_kv, a_dim, a_vdim, window, rot_a, v_mix=rng.random() < 0.7, softcap=softcap,
+                              scale=scale, ff=ff))
+        else:
+            layers.append(ret(r_heads, r_dim, r_vdim, [1.0 - 2.0 ** -rng.uniform(2, 10) for _ in range(r_heads)], rot_r, ff=ff))
+    cfg = TipezenConfig("Tipezen", vocab_size=rng.choice([97, 256, 311, 1000]), hidden_size=W, streams=S,
+                        norm_eps=rng.choice([1e-6, 1e-5]), layers=tuple(layers))
+    return cfg, rng.choice([8, 16, 32]), [rng.randint(1, 40), rng.randint(60, 200), rng.randint(2, 330), rng.randint(20, 90)]
+
+
+@pytest.mark.parametrize("seed", list(range(1, 25)))
+def test_random_configuration_matches_plain(seed):
+    cfg, page, prompts = draw(seed)
+    sd = weights(cfg, seed=seed, sharp=3.0)
+    rng = random.Random(50 + seed)
+    reqs = {f"r{i}": [rng.randrange(cfg.vocab_size) for _ in range(n + 5)] for i, n in enumerate(prompts)}
+    cj = cfg.to_json_dict()
+    want = {r: P.forward(cj, sd, t) for r, t in reqs.items()}
+    # Random hyper-connections can make a position ill-conditioned (streams that nearly cancel in a read).  The bar of a
+    # position is therefore the usual one or, where that is larger, four times what rounding alone does to the plain
+    # implementation there: run in float32 throughout, or with every sublayer's input rounded to bfloat16.
+    rel = lambda a, b: ((a.double() - b).abs() / b.abs().amax(-1, keepdim=True)).amax(-1)
+    bar = {"float32": {r: (4 * rel(P.forward(cj, sd, t, dtype=torch.float32), want[r])).clamp_min(TOL["float32"])
+                       for r, t in reqs.items()},
+           "bfloat16": {r: (4 * rel(P.forward(cj, sd, t, round_inputs=True), want[r])).clamp_min(TOL["bfloat16"])
+                        for r, t in reqs.items()}}
+    most = max(-(-len(t) // page) * page for t in reqs.values())
+    pool = most + most // 2
+    for dtype in ("float32", "bfloat16"):
+        for steps, tokens in ((trace_mixed(reqs, prompts, max_live=3, page_size=page, pool_tokens=pool, chunk=48), pool),
+                              (trace_portions(reqs, sizes=(64, 2, 17, 130, 3)), most)):
+            got = run_trace(runner_of(cfg, sd, dtype, page, tokens, live=3), reqs, steps, poison=True)
+            for q in reqs:
+                err = torch.nan_to_num(rel(got[q], want[q]), nan=float("inf"))
+                bad = (err > bar[dtype][q]).nonzero()
+                assert bad.numel() == 0, (f"draw {seed} {dtype}: request {q} token {int(bad[0])} off by "
+                                          f"{float(err[int(bad[0])]):.3g} (bar {float(bar[dtype][q][int(bad[0])]):.3g}): {cj}")
