@@ -532,7 +532,8 @@ def run_tipezen(steps: int, warmup: int) -> int:
                 finish_b = lambda T: nl * T * ((2 * RH * D + 2 * RH * D) * 4 + (2 * RH * D) * 4) + \
                     nl * T * ((H + 2 * G) * D * 4 + H * D * 2 + 2 * G * D * 2 + 2 * G * D * 4)
                 state_b = nl * 8 * RH * D * D * 4 * 2          # decode: every request's state read and written
-                ret_flops = lambda T: nl * RH * T * 2.0 * (D * D * 2 + 32 * D + 32 * D / 2.0 + D * D)   # chunks of 32
+                # chunks of 64 tokens: A = Q K^T and A V (64 x 64 x D each), U = K^T V and Q S (64 x D x D each)
+                ret_flops = lambda T: nl * RH * (T / 64.0) * 2.0 * 64 * D * (2 * 64 + 2 * D)
                 fr = {}
                 for step, T in (("prefill", P), ("decode", 8)):
                     k = kinds.get(step) or {}
