@@ -429,9 +429,9 @@ def tipezen_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, st
     from tffinfer_b200.config import TipezenConfig, TipezenLayer, RotaryConfig
     from tffinfer_b200.weights import random_tensors_on_device
     W, H, G, D, F, win, RH = TIPEZEN_SIZES[size]
-    att = TipezenLayer(type="attention", heads=H, kv_heads=G, dim=D, vdim=D, scale=D ** -0.5, softcap=30.0, window=win,
-                       v_mix=True, rot=RotaryConfig(1e4, D, (8.0, 2048.0, 32.0, 1.0)), ff=F)
-    ret = TipezenLayer(type="retention", heads=RH, dim=D, vdim=D, rot=RotaryConfig(1e6, D),
+    att = TipezenLayer(type="attention", heads=H, kv_heads=G, dim=D, vdim=D, scale=D ** -0.5, softcap=50.0, window=win,
+                       v_mix=True, rot=RotaryConfig(5e4, D, (4.0, 4096.0, 16.0, 1.0)), ff=F)
+    ret = TipezenLayer(type="retention", heads=RH, dim=D, vdim=D, rot=RotaryConfig(5e5, D),
                        decay=tuple(1.0 - 2.0 ** (-5 - 4 * i / RH) for i in range(RH)))
     cfg = TipezenConfig("Tipezen", vocab_size=TIPEZEN_VOCAB, hidden_size=W, streams=4, norm_eps=1e-6,
                         layers=tuple(ret if i % 2 == 0 else att for i in range(TIPEZEN_LAYERS)))

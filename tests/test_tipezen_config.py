@@ -88,7 +88,7 @@ def test_random_model_folder(tmp_path):
     assert logits.shape == (11, 50) and layers.shape == (4, 11, 24) and torch.isfinite(logits).all()
 
 
-@pytest.mark.parametrize("rot", [RotaryConfig(1e4, 64), RotaryConfig(1e6, 32, (8.0, 2048.0, 32.0, 1.0)),
+@pytest.mark.parametrize("rot", [RotaryConfig(1e4, 64), RotaryConfig(1e6, 32, (16.0, 1024.0, 24.0, 1.0)),
                                  RotaryConfig(500.0, 6, (2.5, 40.0, 3.0, 0.7))])
 def test_frequencies_match_the_plain_ones(rot):
     f, mag = scaled_frequencies(rot.dims, rot.base, rot.scaling)
