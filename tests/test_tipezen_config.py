@@ -66,7 +66,9 @@ def test_description_names_needs_and_groups():
                      "l0.hc1.mix": (3, 3), "l0.ls1": (24,), "l1.mix.g": (4, 24), "l1.mix.vmix": (), "l2.mix.vmix": (),
                      "l1.mix.v": (24, 24), "l1.mlp.gate": (24, 24), "l1.hc2.in": (3,), "l3.mix.q": (32, 24)}.items():
         assert tuple(names[n].shape) == shape, n
-    assert "l0.norm2" not in names and "l0.hc2.in" not in names and "l3.mix.vmix" not in names and "l2.mlp.up" not in names
+    assert "l0.norm2" not in names and "l0.hc2.in" not in names and "l2.mlp.up" not in names
+    # a layer that mixes no values may carry the scalar or not; a layer that does must
+    assert names["l3.mix.vmix"].optional and not names["l1.mix.vmix"].optional and not names["l2.mix.vmix"].optional
     needs = model.cache_needs()
     assert needs[0] == StateNeed((2, 8, 4), "float32")
     assert needs[1] == KVNeed(2, 12, 7) and needs[2] == KVNeed(2, 12, 0) and needs[3] == KVNeed(1, 16, 3)
@@ -84,6 +86,15 @@ def test_random_model_folder(tmp_path):
     assert TipezenConfig.from_json_dict(read_config_json(d)) == cfg
     f = SafetensorsFile(str(tmp_path / "m" / "model.safetensors"))
     w = {n: f.tensor(n).clone() for n in f.names()}
+    assert "l3.mix.vmix" not in w and "l1.mix.vmix" in w
+    # the loader's checks: an optional tensor may be there or not, a required one must
+    from tffinfer_b200.weights.loader import check_tensors, WeightError
+    expected = Model(tff.get_architecture("Tipezen").describe(cfg)).expected_tensors()
+    assert "l3.mix.vmix" not in check_tensors(w, expected, torch.float32, "cpu")
+    assert "l3.mix.vmix" in check_tensors({**w, "l3.mix.vmix": torch.zeros(())}, expected, torch.float32, "cpu")
+    with pytest.raises(WeightError) as e:
+        check_tensors({n: t for n, t in w.items() if n != "l2.mix.vmix"}, expected, torch.float32, "cpu")
+    assert "l2.mix.vmix" in str(e.value)
     logits, layers = P.forward(cfg.to_json_dict(), w, [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], return_layers=True)
     assert logits.shape == (11, 50) and layers.shape == (4, 11, 24) and torch.isfinite(logits).all()
 

@@ -138,8 +138,8 @@ class GatedSinkAttention(Mixer):
              n["o"]: WeightSpec((self.hidden_size, self.num_heads * self.v_head_dim), MATRIX)}
         if self.head_gate:
             s[n["gate"]] = WeightSpec((self.num_heads, self.hidden_size), MATRIX)
-        if self.lambda_tensor:
-            s[n["lambda"]] = WeightSpec((), VECTOR, init="normal", init_scale=0.3)
+        # a layer that mixes nothing may still carry the scalar in a file: it is accepted and not used
+        s[n["lambda"]] = WeightSpec((), VECTOR, init="normal", init_scale=0.3, optional=not self.lambda_tensor)
         return s
 
     def load(self, tensors, ops, act_dtype) -> None:

@@ -24,6 +24,7 @@ class WeightSpec:
     role: str = MATRIX
     init: str = "normal"          # random-weights mode: "normal" | "one_plus_normal" | "eye_plus_normal" | "zeros"
     init_scale: Optional[float] = None   # std; None = the model's init_std (normal) or 0.1 (one_plus_normal)
+    optional: bool = False               # a file may hold it or not (the part does not use it); never made at random
 
 
 # --- cache needs ---------------------------------------------------------------

@@ -79,7 +79,7 @@ class Model:
         self.embed = tensors[d.embed_name]
         self.lm_head = tensors[d.lm_head_name] if d.lm_head_name is not None else self.embed
         for p in self.all_parts():
-            p.load({rel: tensors[p.full_name(rel)] for rel in p.weight_specs()}, ops, act_dtype)
+            p.load({rel: tensors[p.full_name(rel)] for rel in p.weight_specs() if p.full_name(rel) in tensors}, ops, act_dtype)
         for pos in self.positions.values():
             pos.prepare(ops, device, d.max_position)
 

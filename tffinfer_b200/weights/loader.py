@@ -69,7 +69,7 @@ def check_and_load(files: List[SafetensorsFile], expected: Dict[str, WeightSpec]
             if n in where:
                 duplicates.append(n)
             where[n] = f
-    missing = [n for n in expected if n not in where]
+    missing = [n for n in expected if n not in where and not expected[n].optional]
     unexpected = [n for n in where if n not in expected]
     wrong_shape, wrong_dtype = [], []
     for n, spec in expected.items():
@@ -86,6 +86,8 @@ def check_and_load(files: List[SafetensorsFile], expected: Dict[str, WeightSpec]
         raise WeightError(sorted(missing), sorted(unexpected), wrong_shape, wrong_dtype, sorted(set(duplicates)))
     out: Dict[str, torch.Tensor] = {}
     for n, spec in expected.items():
+        if n not in where:
+            continue                      # optional and absent
         t = where[n].tensor(n)
         out[n] = t.to(device=device, dtype=held_dtype(t.dtype, spec.role, compute_dtype)).contiguous()
     return out
@@ -104,7 +106,7 @@ def load_model_weights(model_dir: str, expected: Dict[str, WeightSpec],
 def check_tensors(tensors: Dict[str, torch.Tensor], expected: Dict[str, WeightSpec],
                   compute_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
     """The same checks and dtype policy for tensors that are already in memory."""
-    missing = sorted(n for n in expected if n not in tensors)
+    missing = sorted(n for n in expected if n not in tensors and not expected[n].optional)
     unexpected = sorted(n for n in tensors if n not in expected)
     wrong_shape = [(n, expected[n].shape, tuple(tensors[n].shape)) for n in expected
                    if n in tensors and tuple(tensors[n].shape) != tuple(expected[n].shape)]
@@ -119,4 +121,4 @@ def check_tensors(tensors: Dict[str, torch.Tensor], expected: Dict[str, WeightSp
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(missing, unexpected, wrong_shape, wrong_dtype)
     return {n: tensors[n].to(device=device, dtype=held_dtype(tensors[n].dtype, spec.role, compute_dtype)).contiguous()
-            for n, spec in expected.items()}
+            for n, spec in expected.items() if n in tensors}

@@ -54,7 +54,7 @@ def random_state_dict(cfg: ModelConfig, seed: int, store_dtype: str = "bfloat16"
     model = Model(desc)
     sd = _STORE[store_dtype]
     return {name: random_tensor(seed, name, spec, desc.init_std, norm_noise, sd)
-            for name, spec in model.expected_tensors().items()}
+            for name, spec in model.expected_tensors().items() if not spec.optional}
 
 
 def write_random_model(model_dir: str, cfg: ModelConfig, seed: int, store_dtype: str = "bfloat16",
@@ -80,6 +80,8 @@ def random_tensors_on_device(cfg: ModelConfig, seed: int, device, store_dtype: s
     gen.manual_seed(seed)
     out = {}
     for name, spec in model.expected_tensors().items():
+        if spec.optional:
+            continue
         if spec.role == INT_TABLE:
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif spec.init == "one_plus_normal":
