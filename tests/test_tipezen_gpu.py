@@ -62,9 +62,15 @@ def weights(cfg, seed=11, sharp=4.0):
     """Random weights; the query and key projections are scaled up so that attention is far from uniform and a
     key that is wrongly seen or missed moves the logits."""
     sd = random_state_dict(cfg, seed, "bfloat16", norm_noise=0.2)
+    tame = min(1.0, 3.0 / max(cfg.streams, 1))      # many streams of independent noise nearly cancel in a read
     for n in sd:
         if n.endswith(".mix.q") or n.endswith(".mix.k"):
             sd[n] = (sd[n].float() * sharp).to(torch.bfloat16)
+        elif ".hc" in n and n.endswith(".mix"):
+            eye = torch.eye(sd[n].shape[0])
+            sd[n] = (eye + (sd[n].float() - eye) * tame).to(torch.bfloat16)
+        elif ".hc" in n:
+            sd[n] = (1.0 + (sd[n].float() - 1.0) * tame).to(torch.bfloat16)
     return sd
 
 

@@ -18,6 +18,7 @@
 // the additions that make a token's output depends on its position (and on where a portion was cut), not on what
 // else is in the batch.
 #include "common.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -213,11 +214,13 @@ retention_local_kernel(RetParams p, int num_requests, float* __restrict__ acc, f
     tile_product(skT, C, sv, vP, d, dv, nP, [&](int r, int cc, float a) { Uc[r * dv + cc] = a; });
 }
 
+// VEC = 4: a thread walks four neighbouring state elements (16-byte accesses); 1: one element.
+template <int VEC>
 __global__ void __launch_bounds__(NT)
 retention_scan_kernel(RetParams p, int num_requests, float* __restrict__ U) {
     pdl_launch_dependents();
     const int h = blockIdx.y, b = blockIdx.z;
-    const int e = blockIdx.x * NT + threadIdx.x;
+    const int e = (blockIdx.x * NT + threadIdx.x) * VEC;
     const int t0 = p.q_start[b], len = p.q_start[b + 1] - t0;
     const int slot = p.slots[b];
     const float decay = p.decay[h];
@@ -230,25 +233,33 @@ retention_scan_kernel(RetParams p, int num_requests, float* __restrict__ U) {
     if (len <= 0 || slot < 0 || slot >= p.num_slots || e >= p.d * p.dv) return;
     const int pos0 = p.pos_start[b];
     const int count = (pos0 + len - 1) / C - pos0 / C + 1;
-    float* gs = p.state + ((size_t)slot * p.H + h) * p.d * p.dv + e;
-    float S = *gs;
-    const size_t stride = (size_t)p.H * p.d * p.dv;                   // floats between a chunk's U and the next one's
-    float* u0 = U + ((size_t)first_chunk * p.H + h) * p.d * p.dv + e;
+    typedef typename std::conditional<VEC == 4, float4, float>::type V;
+    V* gs = reinterpret_cast<V*>(p.state + ((size_t)slot * p.H + h) * p.d * p.dv + e);
+    V S = *gs;
+    const size_t stride = (size_t)p.H * p.d * p.dv / VEC;             // V's between a chunk's U and the next one's
+    V* u0 = reinterpret_cast<V*>(U + ((size_t)first_chunk * p.H + h) * p.d * p.dv + e);
+    float g_full = 1.f;
+    for (int i = 0; i < C; ++i) g_full *= decay;                       // the same product as the other kernels' table
     // eight chunks' U are asked for together, then the state walks through them: the loads of a chunk do not wait
     // for the chunk before
     for (int c0 = 0; c0 < count; c0 += 8) {
-        float add[8];
+        V add[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) add[j] = c0 + j < count ? u0[(size_t)(c0 + j) * stride] : 0.f;
+        for (int j = 0; j < 8; ++j) if (c0 + j < count) add[j] = u0[(size_t)(c0 + j) * stride];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int c = c0 + j;
             if (c < count) {
                 const int lo = max(pos0, (pos0 / C + c) * C), hi = min(pos0 + len, (pos0 / C + c + 1) * C);
                 u0[(size_t)c * stride] = S;
-                float g = 1.f;
-                for (int i = 0; i < hi - lo; ++i) g *= decay;          // the same product as the other kernels' table
-                S = fmaf(g, S, add[j]);
+                float g = g_full;
+                if (hi - lo != C) { g = 1.f; for (int i = 0; i < hi - lo; ++i) g *= decay; }
+                if constexpr (VEC == 4) {
+                    S.x = fmaf(g, S.x, add[j].x); S.y = fmaf(g, S.y, add[j].y);
+                    S.z = fmaf(g, S.z, add[j].z); S.w = fmaf(g, S.w, add[j].w);
+                } else {
+                    S = fmaf(g, S, add[j]);
+                }
             }
         }
     }
@@ -372,8 +383,12 @@ TFF_API int tff_retention(
         }
         int st = tff_launch_pdl(retention_local_kernel, dim3(chunks, H), dim3(NT), smem1, stream, p, num_requests, acc, U);
         if (st != TFF_OK) return st;
-        st = tff_launch_pdl(retention_scan_kernel, dim3((d * dv + NT - 1) / NT, H, num_requests), dim3(NT), (size_t)0, stream,
-                            p, num_requests, U);
+        if ((d * dv) % 4 == 0 && ((uintptr_t)state & 15) == 0 && ((uintptr_t)U & 15) == 0)
+            st = tff_launch_pdl(retention_scan_kernel<4>, dim3((d * dv / 4 + NT - 1) / NT, H, num_requests), dim3(NT), (size_t)0,
+                                stream, p, num_requests, U);
+        else
+            st = tff_launch_pdl(retention_scan_kernel<1>, dim3((d * dv + NT - 1) / NT, H, num_requests), dim3(NT), (size_t)0,
+                                stream, p, num_requests, U);
         if (st != TFF_OK) return st;
         if (out_is_bf16)
             return tff_launch_pdl(retention_finish_kernel<bf16>, dim3(chunks, H), dim3(NT), smem3, stream, p, num_requests,

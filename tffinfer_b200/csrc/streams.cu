@@ -4,6 +4,7 @@
 //   write (when y is given):  x'[t] = sum_s mix[s, t] x[s] + out[t] * (scale * y),  all t from the old x[s]
 //   read  (when h is given):  u = sum_s in[s] x'[s];  h = u * rsqrt(mean(u^2) + eps) * w
 //
+// y may be cleared behind the read (it is then one of the accumulator buffers that split products add into).
 // mix, out, in are float32 [S, S], [S], [S]; a null pointer stands for the identity matrix, ones, ones, so
 // S = 1 with null pointers is the plain pre-norm residual with layer scale.  scale and w may be null (ones).
 // One CTA per row; a thread owns columns and holds the S values of a column in registers, so the update
@@ -34,7 +35,7 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float
 template <typename TO, int NT, int MAX_STREAMS>
 __global__ void __launch_bounds__(NT)
 stream_step_kernel(float* __restrict__ x, int S, int W,
-                   const float* __restrict__ y, const float* __restrict__ scale,
+                   float* __restrict__ y, int clear_y, const float* __restrict__ scale,
                    const float* __restrict__ mix, const float* __restrict__ outw,
                    const float* __restrict__ inw, const float* __restrict__ w, float eps,
                    const int* __restrict__ row_index, TO* __restrict__ h, float* __restrict__ total) {
@@ -54,7 +55,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
     __syncthreads();
     pdl_wait();
     float* xr = x + (size_t)row * S * W;
-    const float* yr = y ? y + (size_t)row * W : nullptr;
+    float* yr = y ? y + (size_t)row * W : nullptr;
     float ss = 0.f;
     // four columns a thread at a time (16-byte accesses) when the rows allow it; which path runs depends on W and
     // the buffers' alignment alone, so a row's sums are always added in the same order
@@ -69,6 +70,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                 v[s] = s < S ? reinterpret_cast<const float4*>(xr + (size_t)s * W)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (yr) {
                 float4 ys = reinterpret_cast<const float4*>(yr)[i];
+                if (clear_y) reinterpret_cast<float4*>(yr)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (scale) {
                     const float4 g = reinterpret_cast<const float4*>(scale)[i];
                     ys.x *= g.x; ys.y *= g.y; ys.z *= g.z; ys.w *= g.w;
@@ -129,6 +131,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
         for (int s = 0; s < MAX_STREAMS; ++s) v[s] = s < S ? xr[(size_t)s * W + i] : 0.f;
         if (yr) {
             const float ys = scale ? yr[i] * scale[i] : yr[i];
+            if (clear_y) yr[i] = 0.f;
             float n[MAX_STREAMS];
 #pragma unroll
             for (int t = 0; t < MAX_STREAMS; ++t) {
@@ -180,7 +183,9 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const TW* _
 
 // x [rows_total, S, W] float32 (updated in place when y is given); y [rows_total, W] float32 or null;
 // h [rows, W] of the activation type or null; total [rows, W] float32 or null (the combined row itself).
-TFF_API int tff_stream_step(float* x, int S, int W, const float* y, const float* scale, const float* mix,
+// clear_y != 0: the rows of y that were read are set to zero (y is then an accumulator buffer that the next split
+// product adds into).
+TFF_API int tff_stream_step(float* x, int S, int W, float* y, int clear_y, const float* scale, const float* mix,
                             const float* outw, const float* inw, const float* w, float eps, const int* row_index,
                             void* h, int h_is_bf16, float* total, int rows, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
@@ -205,7 +210,7 @@ TFF_API int tff_stream_step(float* x, int S, int W, const float* y, const float*
                 configured = true;                                                                             \
             }                                                                                                  \
         }                                                                                                      \
-        return tff_launch_pdl(kern, dim3(rows), dim3(NT), smem, stream, x, S, W, y, scale, mix, outw, inw, w,  \
+        return tff_launch_pdl(kern, dim3(rows), dim3(NT), smem, stream, x, S, W, y, clear_y, scale, mix, outw, inw, w, \
                               eps, row_index, (TO*)h, total);                                                  \
     } while (0)
     if (W >= 1024) {

@@ -213,6 +213,8 @@ class CudaKernels:
         self._check(self.lib.tff_gemm_simt(_ptr(a), _c_int(_dt(a)), _ptr(w), _c_int(_dt(w)), _ptr(out),
                                            _c_int(_dt(out)), _ptr(residual), _c_int(M), _c_int(N), _c_int(K),
                                            self._stream()), "gemm_simt")
+        if out.data_ptr() in self._acc_zero:
+            self._acc_zero[out.data_ptr()] = False     # an accumulator buffer that now holds a product
         self.launches += 1
 
     FOLD_MAX_M = 16           # up to this many rows the norm is folded into the gate/up product (with SwiGLU)
@@ -381,6 +383,12 @@ class CudaKernels:
             self._acc_zero[buf.data_ptr()] = True
         return buf
 
+    def sublayer_output(self, rows: int, width: int, device, act_dtype) -> torch.Tensor:
+        """A float32 [rows, width] buffer for a sublayer's output that a connector consumes (``stream_step`` clears it
+        behind the read): for decode-sized bfloat16 steps one of the accumulator buffers, so that the split product
+        that writes it needs no clearing kernel; else plain scratch."""
+        return self.projection_buffer(rows, width, device, act_dtype)
+
     def reset_accumulators(self) -> None:
         """After a step that was cut short: every accumulator buffer back to zero."""
         for buf in self._accumulators.values():
@@ -494,10 +502,15 @@ class CudaKernels:
             assert tuple(h.shape) == (rows, W)
         if total is not None:
             assert tuple(total.shape) == (rows, W)
-        self._check(self.lib.tff_stream_step(_ptr(x), _c_int(S), _c_int(W), _ptr(y), _ptr(scale), _ptr(mix), _ptr(out),
+        # a y that is one of the accumulator buffers kept at zero is cleared behind the read; when only some rows are
+        # read (row_index), the others stay as they are and the buffer counts as used
+        clear = 1 if (y is not None and y.data_ptr() in self._acc_zero) else 0
+        self._check(self.lib.tff_stream_step(_ptr(x), _c_int(S), _c_int(W), _ptr(y), _c_int(clear), _ptr(scale), _ptr(mix), _ptr(out),
                                              _ptr(read), _ptr(norm_weight), _c_float(eps), _ptr(row_index), _ptr(h),
                                              _c_int(_dt(h)) if h is not None else _c_int(0), _ptr(total), _c_int(rows),
                                              self._stream()), "stream_step")
+        if clear:
+            self._acc_zero[y.data_ptr()] = row_index is None
         self.launches += 1
 
     # ------------------------------------------------------- mixers with a rotation computed on the fly

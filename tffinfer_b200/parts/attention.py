@@ -178,7 +178,7 @@ class GatedSinkAttention(Mixer):
                          self.lam if self.value_mix == "mix" else None,
                          self.gate_off if self.head_gate else -1, ctx.write_cache)
         if residual is None:
-            out = torch.empty((T, self.hidden_size), dtype=torch.float32, device=h.device)
+            out = ops.sublayer_output(T, self.hidden_size, h.device, h.dtype)
             ops.gemm(attn, self.w_o, out)
             return out
         ops.gemm(attn, self.w_o, residual, residual=residual)

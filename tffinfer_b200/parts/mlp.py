@@ -50,7 +50,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx, residual):
         if residual is None:              # f(h) alone, for arrangements that do more with it than add it
-            out = torch.empty((h.shape[0], self.hidden_size), dtype=torch.float32, device=h.device)
+            out = ctx.ops.sublayer_output(h.shape[0], self.hidden_size, h.device, h.dtype)
             ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, None, self.intermediate_size,
                               activation=self.activation, out=out)
             return out

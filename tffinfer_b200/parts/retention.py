@@ -71,7 +71,7 @@ class Retention(Mixer):
         ops.retain(h, self.w_in, freq, ctx.batch, ctx.state, self.decay_dev, mixed, self.num_heads, self.head_dim,
                    self.v_head_dim, float(self.head_dim) ** -0.5, self.eps)
         if residual is None:
-            out = torch.empty((T, self.hidden_size), dtype=torch.float32, device=h.device)
+            out = ops.sublayer_output(T, self.hidden_size, h.device, h.dtype)
             ops.gemm(mixed, self.w_o, out)
             return out
         ops.gemm(mixed, self.w_o, residual, residual=residual)
