@@ -179,6 +179,14 @@ def test_stream_step(ops, S, W):
     ops.stream_step(xd2, read=rd.cuda(), norm_weight=w.cuda(), eps=1e-5, h=h2, row_index=rows)
     assert torch.equal(xd2, xd)
     assert torch.allclose(h2.float().cpu().double(), want_h[[7, 0, 3]], rtol=1e-2, atol=1e-2)
+    # write and read at chosen rows, one of them twice: the streams stay as they were, the rows' h is that of the write
+    xd3 = x.cuda()
+    rows = torch.tensor([5, 2, 5], dtype=torch.int32, device="cuda")
+    h3 = torch.empty(3, W, device="cuda")
+    ops.stream_step(xd3, y=y.cuda(), scale=scale.cuda(), mix=mix.cuda(), out=out.cuda(), read=rd.cuda(),
+                    norm_weight=w.cuda(), eps=1e-5, h=h3, row_index=rows)
+    assert torch.equal(xd3.cpu(), x)
+    assert torch.allclose(h3.cpu().double(), want_h[[5, 2, 5]], rtol=1e-4, atol=1e-5)
 
 
 @pytest.mark.parametrize("pairing", ["interleaved", "halves"])

@@ -10,8 +10,9 @@
 // One CTA per row; a thread owns columns and holds the S values of a column in registers, so the update
 // is in place.  Every sum runs over s in ascending order and the row's sum of squares is reduced in an order that
 // depends on W alone: a row's result does not depend on what else is in the batch.
-// With row_index, CTA r works on row row_index[r] (both parts), and h is written to row r: the last
-// sublayer's write and the model's final norm only ever matter at the rows whose logits are wanted.
+// With row_index, CTA r works on row row_index[r] (both parts) and h is written to row r; the row's new streams
+// feed h and are not stored (a row may be listed twice): the last sublayer's write and the model's final norm only
+// ever matter at the rows whose logits are wanted, and the streams live for one step.
 #include "common.cuh"
 
 namespace {
@@ -56,6 +57,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
     pdl_wait();
     float* xr = x + (size_t)row * S * W;
     float* yr = y ? y + (size_t)row * W : nullptr;
+    const bool store_x = row_index == nullptr;       // chosen rows: the new streams feed h and are not kept
     float ss = 0.f;
     // four columns a thread at a time (16-byte accesses) when the rows allow it; which path runs depends on W and
     // the buffers' alignment alone, so a row's sums are always added in the same order
@@ -91,7 +93,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                 }
 #pragma unroll
                 for (int t = 0; t < MAX_STREAMS; ++t)
-                    if (t < S) { v[t] = n[t]; reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = n[t]; }
+                    if (t < S) { v[t] = n[t]; if (store_x) reinterpret_cast<float4*>(xr + (size_t)t * W)[i] = n[t]; }
             }
             if (h || total) {
                 float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -141,7 +143,7 @@ stream_step_kernel(float* __restrict__ x, int S, int W,
                 n[t] = t < S ? fmaf(c_out[t], ys, a) : 0.f;
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) if (t < S) { v[t] = n[t]; xr[(size_t)t * W + i] = n[t]; }
+            for (int t = 0; t < MAX_STREAMS; ++t) if (t < S) { v[t] = n[t]; if (store_x) xr[(size_t)t * W + i] = n[t]; }
         }
         if (h || total) {
             float u = 0.f;

@@ -484,7 +484,8 @@ class CudaKernels:
         out[t] * (scale * y) in place (mix [S, S], out [S], scale [W]; None = identity, ones, ones).  With ``h``
         ([rows, W], activation type): h = rmsnorm(sum_s read[s] x_s) with ``norm_weight`` and ``eps`` (read None = ones).
         With ``total`` (float32 [rows, W]): the combined row itself.  ``row_index`` (int32 [rows]) limits all of it to
-        those rows of x; h and total are then indexed by the place in ``row_index``."""
+        those rows of x; h and total are then indexed by the place in ``row_index``, and x itself is left as it was
+        (the new streams of those rows feed h only)."""
         self._need_cuda(x, y, scale, mix, out, read, norm_weight, h, row_index, total)
         T, S, W = x.shape
         assert x.dtype == torch.float32
@@ -503,14 +504,15 @@ class CudaKernels:
         if total is not None:
             assert tuple(total.shape) == (rows, W)
         # a y that is one of the accumulator buffers kept at zero is cleared behind the read; when only some rows are
-        # read (row_index), the others stay as they are and the buffer counts as used
-        clear = 1 if (y is not None and y.data_ptr() in self._acc_zero) else 0
+        # read (row_index; a row may be listed twice), nothing is cleared and the buffer counts as used
+        kept_zero = y is not None and y.data_ptr() in self._acc_zero
+        clear = 1 if (kept_zero and row_index is None) else 0
         self._check(self.lib.tff_stream_step(_ptr(x), _c_int(S), _c_int(W), _ptr(y), _c_int(clear), _ptr(scale), _ptr(mix), _ptr(out),
                                              _ptr(read), _ptr(norm_weight), _c_float(eps), _ptr(row_index), _ptr(h),
                                              _c_int(_dt(h)) if h is not None else _c_int(0), _ptr(total), _c_int(rows),
                                              self._stream()), "stream_step")
-        if clear:
-            self._acc_zero[y.data_ptr()] = row_index is None
+        if kept_zero:
+            self._acc_zero[y.data_ptr()] = bool(clear)
         self.launches += 1
 
     # ------------------------------------------------------- mixers with a rotation computed on the fly

@@ -56,7 +56,8 @@ class ResidualStreams:
 
     def read(self, read_w, norm, ops, out_dtype, row_index=None) -> torch.Tensor:
         """norm(sum_s read_w[s] x_s) at every row, or at the rows of ``row_index``; applies the write that is
-        still to come in the same kernel (with ``row_index``, at those rows only)."""
+        still to come in the same kernel.  With ``row_index`` the write feeds the read of those rows only and the
+        streams are not updated: that is the model's last read, nothing looks at them afterwards."""
         rows = self.x.shape[0] if row_index is None else row_index.shape[0]
         h = torch.empty((rows, self.x.shape[2]), dtype=out_dtype, device=self.x.device)
         y, scale, mix, out = self.pending if self.pending is not None else (None, None, None, None)
