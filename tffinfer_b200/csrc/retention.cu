@@ -132,18 +132,22 @@ __device__ inline bool find_chunk(const RetParams& p, int num_requests, int inde
 
 // out(m, n) = sum_k A[m][k] B[k][n] for m < M, n < N; K a multiple of 4; rows of A up to pad4(M) and columns of B up
 // to pad4(N) are readable.  Consecutive threads take consecutive column tiles.
+// ``lower``: 0 = nothing known; 1 = only outputs with n <= m are wanted (tiles above the diagonal are left out);
+// 2 = A is lower triangular (A[m][k] = 0 for k > m: the sum stops at the tile's last row).
 template <typename F>
 __device__ __forceinline__ void tile_product(const float* __restrict__ A, int lda, const float* __restrict__ B, int ldb,
-                                             int M, int N, int K, F&& store) {
+                                             int M, int N, int K, F&& store, int lower = 0) {
     const int tn = (N + 3) >> 2, tm = (M + 3) >> 2;
     for (int tile = threadIdx.x; tile < tm * tn; tile += NT) {
         const int m0 = (tile / tn) << 2, n0 = (tile % tn) << 2;
+        if (lower == 1 && n0 > m0 + 3) continue;
+        const int kend = lower == 2 ? min(K, m0 + 4) : K;
         float acc[4][4];
 #pragma unroll
         for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
-        for (int k = 0; k < K; k += 4) {
+        for (int k = 0; k < kend; k += 4) {
             float4 a[4], b[4];
 #pragma unroll
             for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4*>(A + (m0 + r) * lda + k);
@@ -202,11 +206,12 @@ retention_local_kernel(RetParams p, int num_requests, float* __restrict__ acc, f
         if (p.clear) p.vg[(size_t)(c.t + i) * p.ld + p.v_off + h * dv + r] = 0.f;
     }
     __syncthreads();
-    tile_product(sq, dP, skT, C, n, n, dP, [&](int i, int j, float a) { sA[i * C + j] = j <= i ? a * pw[i - j] : 0.f; });
+    // (sA was cleared above: the tiles above the diagonal, which are left out, hold zeros)
+    tile_product(sq, dP, skT, C, n, n, dP, [&](int i, int j, float a) { sA[i * C + j] = j <= i ? a * pw[i - j] : 0.f; }, 1);
     __syncthreads();
     tile_product(sA, C, sv, vP, n, dv, nP, [&](int i, int r, float a) {
         acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + r] = a;
-    });
+    }, 2);
     __syncthreads();                                                  // every thread is done with skT as it was
     for (int e = threadIdx.x; e < d * n; e += NT) { const int r = e / n, j = e % n; skT[r * C + j] *= pw[n - 1 - j]; }
     __syncthreads();
