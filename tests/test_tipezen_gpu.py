@@ -465,3 +465,22 @@ def test_random_configuration_matches_plain(seed):
                 bad = (err > bar[dtype][q]).nonzero()
                 assert bad.numel() == 0, (f"draw {seed} {dtype}: request {q} token {int(bad[0])} off by "
                                           f"{float(err[int(bad[0])]):.3g} (bar {float(bar[dtype][q][int(bad[0])]):.3g}): {cj}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_graph_replay(dtype):
+    """Two requests decoded for 300 tokens, one token a step, the steps replayed as CUDA graphs: the windows pass over
+    decoded tokens many times, pages are given back behind them, and the retention state is carried all the way."""
+    cfg = config("a")
+    sd = weights(cfg)
+    rng = random.Random(4)
+    reqs = {r: [rng.randrange(cfg.vocab_size) for _ in range(n + 300)] for r, n in (("r0", 21), ("r1", 3))}
+    want = {r: P.forward(cfg.to_json_dict(), sd, t) for r, t in reqs.items()}
+    steps = [([("r0", 0, 21), ("r1", 0, 3)], [])]
+    steps += [([("r0", 21 + i, 1), ("r1", 3 + i, 1)], ["r0", "r1"] if i == 299 else []) for i in range(300)]
+    r = runner_of(cfg, sd, dtype, 16, 2 * 336, live=2, graphs=True)
+    got = run_trace(r, reqs, steps, poison=True)
+    assert any(st["graphs"] for st in r._graphs.values()), "the decode steps were not replayed as graphs"
+    for q in reqs:
+        bad = first_bad(got[q], want[q], TOL[dtype])
+        assert bad is None, f"{dtype}: request {q} token {bad[0]} off by {bad[1]:.3g}"
