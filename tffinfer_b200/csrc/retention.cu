@@ -38,7 +38,6 @@ struct RetParams {
 template <typename TO, bool IN_SMEM>
 __global__ void __launch_bounds__(NT)
 retention_step_kernel(RetParams p) {
-    constexpr bool state_in_smem = IN_SMEM;
     extern __shared__ float sm[];
     pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
@@ -46,11 +45,11 @@ retention_step_kernel(RetParams p) {
     float* S;
     if constexpr (IN_SMEM) S = sm;
     else S = p.state + ((size_t)min(max(p.slots[b], 0), p.num_slots - 1) * p.H + h) * d * dv;
-    float* sq = sm + (state_in_smem ? d * dv : 0);   // [d]
+    float* sq = sm + (IN_SMEM ? d * dv : 0);   // [d]
     float* sk = sq + d;                 // [d]
     float* sv = sk + d;                 // [dv]
     float* part = sv + dv;              // [NY][dv]
-    float* red = part + (NT / 1) ;      // generous: NY * dv <= NT
+    float* red = part + NT;             // NY * dv <= NT
     const int NY = NT / dv > 0 ? NT / dv : 1;
     const int j = threadIdx.x % dv, ty = threadIdx.x / dv;
     const bool active = ty < NY && dv <= NT;
@@ -60,7 +59,7 @@ retention_step_kernel(RetParams p) {
     pdl_wait();
     if (t1 <= t0 || slot < 0 || slot >= p.num_slots) return;
     float* gs = p.state + ((size_t)slot * p.H + h) * d * dv;
-    if (state_in_smem) for (int e = threadIdx.x; e < d * dv; e += NT) S[e] = gs[e];
+    if (IN_SMEM) for (int e = threadIdx.x; e < d * dv; e += NT) S[e] = gs[e];
     for (int t = t0; t < t1; ++t) {
         __syncthreads();
         for (int i = threadIdx.x; i < d; i += NT) {
@@ -95,7 +94,7 @@ retention_step_kernel(RetParams p) {
         }
     }
     __syncthreads();
-    if (state_in_smem) for (int e = threadIdx.x; e < d * dv; e += NT) gs[e] = S[e];
+    if (IN_SMEM) for (int e = threadIdx.x; e < d * dv; e += NT) gs[e] = S[e];
 }
 
 // ------------------------------------------------------------------ chunk by chunk
