@@ -269,7 +269,7 @@ def test_attention_window_edges_cap_and_sink(ops, dtype, lens, starts):
     assert torch.allclose(got, want, rtol=tol, atol=tol)
 
 
-@pytest.mark.parametrize("H,d,dv", [(2, 64, 32), (1, 12, 28), (3, 128, 128), (1, 256, 64)])
+@pytest.mark.parametrize("H,d,dv", [(2, 64, 32), (1, 12, 28), (3, 128, 128), (1, 256, 64), (1, 16, 320), (1, 256, 256)])
 def test_retention_steps_chunks_and_far_keys(ops, H, d, dv):
     """The recurrence token by token and chunk by chunk against the plain loop: requests at different places of
     their sequences, states in slots out of order, one far key that a slow decay must still carry."""

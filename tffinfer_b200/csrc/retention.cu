@@ -49,10 +49,11 @@ retention_step_kernel(RetParams p) {
     float* sk = sq + d;                 // [d]
     float* sv = sk + d;                 // [dv]
     float* part = sv + dv;              // [NY][dv]
-    float* red = part + NT;             // NY * dv <= NT
-    const int NY = NT / dv > 0 ? NT / dv : 1;
-    const int j = threadIdx.x % dv, ty = threadIdx.x / dv;
-    const bool active = ty < NY && dv <= NT;
+    const int JW = min(dv, NT);         // value columns worked on side by side, by NY groups of rows each
+    const int NY = NT / JW;
+    float* red = part + NY * dv;
+    const int j0 = threadIdx.x % JW, ty = threadIdx.x / JW;
+    const bool active = ty < NY;
     const int t0 = p.q_start[b], t1 = p.q_start[b + 1];
     const int slot = p.slots[b];
     const float decay = p.decay[h];
@@ -72,25 +73,31 @@ retention_step_kernel(RetParams p) {
         }
         __syncthreads();
         if (active) {
-            float acc = 0.f;
-            const float vj = sv[j];
-            for (int i = ty; i < d; i += NY) {
-                const float s = fmaf(decay, S[i * dv + j], sk[i] * vj);
-                S[i * dv + j] = s;
-                acc = fmaf(s, sq[i], acc);
+            for (int j = j0; j < dv; j += JW) {
+                float acc = 0.f;
+                const float vj = sv[j];
+                for (int i = ty; i < d; i += NY) {
+                    const float s = fmaf(decay, S[i * dv + j], sk[i] * vj);
+                    S[i * dv + j] = s;
+                    acc = fmaf(s, sq[i], acc);
+                }
+                part[ty * dv + j] = acc;
             }
-            part[ty * dv + j] = acc;
         }
         __syncthreads();
-        float o = 0.f;
-        if (threadIdx.x < dv) for (int y = 0; y < NY; ++y) o += part[y * dv + threadIdx.x];
-        const float ss = block_sum<NT>(threadIdx.x < dv ? o * o : 0.f, red);
-        if (threadIdx.x < dv) {
-            const float rs = rsqrtf(ss / (float)dv + p.eps);
-            const float g = p.vg[(size_t)t * p.ld + p.g_off + h * dv + threadIdx.x];
-            if (p.clear) p.vg[(size_t)t * p.ld + p.g_off + h * dv + threadIdx.x] = 0.f;
-            ((TO*)p.out)[(size_t)t * p.H * dv + (size_t)h * dv + threadIdx.x] =
-                from_f32<TO>((o * rs) * (g / (1.0f + expf(-g))));
+        float sq_sum = 0.f;
+        for (int j = threadIdx.x; j < dv; j += NT) {
+            float o = 0.f;
+            for (int y = 0; y < NY; ++y) o += part[y * dv + j];
+            part[j] = o;                                          // row 0 now holds the outputs (only this thread reads column j)
+            sq_sum = fmaf(o, o, sq_sum);
+        }
+        const float ss = block_sum<NT>(sq_sum, red);
+        const float rs = rsqrtf(ss / (float)dv + p.eps);
+        for (int j = threadIdx.x; j < dv; j += NT) {
+            const float g = p.vg[(size_t)t * p.ld + p.g_off + h * dv + j];
+            if (p.clear) p.vg[(size_t)t * p.ld + p.g_off + h * dv + j] = 0.f;
+            ((TO*)p.out)[(size_t)t * p.H * dv + (size_t)h * dv + j] = from_f32<TO>((part[j] * rs) * (g / (1.0f + expf(-g))));
         }
     }
     __syncthreads();
@@ -400,8 +407,7 @@ TFF_API int tff_retention(
         return tff_launch_pdl(retention_finish_kernel<float>, dim3(chunks, H), dim3(NT), smem3, stream, p, num_requests,
                               (const float*)acc, (const float*)U);
     }
-    if (dv > NT) return TFF_ERR_UNSUPPORTED;
-    const size_t rest = sizeof(float) * ((size_t)2 * d + dv + NT + 32);
+    const size_t rest = sizeof(float) * ((size_t)2 * d + dv + (size_t)(NT / (dv < NT ? dv : NT)) * dv + 32);
     const int in_smem = sizeof(float) * (size_t)d * dv + rest <= MOST ? 1 : 0;
     const size_t smem = rest + (in_smem ? sizeof(float) * (size_t)d * dv : 0);
     if (smem > MOST) return TFF_ERR_UNSUPPORTED;
