@@ -24,6 +24,19 @@ namespace {
 
 constexpr int NT = 256;
 
+// four consecutive outputs in one store
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
 struct RetParams {
     const float* q; const float* k; float* vg; int ld, v_off, g_off;
     int clear;                         // v and g are set to zero behind the read (the rows are an accumulator buffer)
@@ -286,6 +299,7 @@ __global__ void __launch_bounds__(NT)
 retention_finish_kernel(RetParams p, int num_requests, const float* __restrict__ acc, const float* __restrict__ U) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float pw[C + 1];
+    __shared__ float srs[C];             // the rows' 1 / rms
     pdl_launch_dependents();
     const int h = blockIdx.y, d = p.d, dv = p.dv, dP = pad4(d), vP = pad4(dv);
     float* sq = sm;                      // [C][dP]
@@ -313,6 +327,16 @@ retention_finish_kernel(RetParams p, int num_requests, const float* __restrict__
         __syncthreads();
         for (int e = threadIdx.x; e < n * d; e += NT) sq[(e / d) * dP + e % d] = qg[(size_t)(e / d) * p.H * d + e % d];
     }
+    // the chunk's local part goes into the output tile first (the product below adds to it): loads asked for together
+    // here, not one by one between the product's stores
+    const float* ag = acc + (size_t)c.t * p.H * dv + (size_t)h * dv;
+    if (vec && (((uintptr_t)acc) & 15) == 0) {
+        const int v4 = dv >> 2;
+        for (int e = threadIdx.x; e < n * v4; e += NT)
+            reinterpret_cast<float4*>(so + (e / v4) * vP)[e % v4] = reinterpret_cast<const float4*>(ag + (size_t)(e / v4) * p.H * dv)[e % v4];
+    } else {
+        for (int e = threadIdx.x; e < n * dv; e += NT) so[(e / dv) * vP + e % dv] = ag[(size_t)(e / dv) * p.H * dv + e % dv];
+    }
     for (int n0 = 0; n0 < dv; n0 += NB) {
         const int nb = min(NB, dv - n0);
         __syncthreads();                                              // the block before has been multiplied
@@ -330,11 +354,46 @@ retention_finish_kernel(RetParams p, int num_requests, const float* __restrict__
         }
         __syncthreads();
         tile_product(sq, dP, sS, NB, n, nb, dP, [&](int i, int r, float a) {
-            so[i * vP + n0 + r] = fmaf(pw[i + 1], a, acc[(size_t)(c.t + i) * p.H * dv + (size_t)h * dv + n0 + r]);
+            so[i * vP + n0 + r] = fmaf(pw[i + 1], a, so[i * vP + n0 + r]);
         });
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* gg = p.vg + (size_t)c.t * p.ld + p.g_off + h * dv;         // the chunk's gates, rows ld apart
+    if (vec && (p.ld & 3) == 0 && (((uintptr_t)gg | (uintptr_t)p.out) & 15) == 0) {
+        // the rows' scales, a warp per token, then all elements with the gates asked for eight loads at a time
+        for (int i = warp; i < n; i += NT / 32) {
+            float ss = 0.f;
+            for (int r = lane; r < dv; r += 32) ss = fmaf(so[i * vP + r], so[i * vP + r], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) srs[i] = rsqrtf(ss / (float)dv + p.eps);
+        }
+        __syncthreads();
+        const int v4 = dv >> 2, total4 = n * v4;
+        TO* og = (TO*)p.out + (size_t)c.t * p.H * dv + (size_t)h * dv;
+        for (int e0 = threadIdx.x; e0 < total4; e0 += NT * 8) {
+            float4 g[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int e = e0 + k * NT;
+                if (e < total4) g[k] = reinterpret_cast<const float4*>(gg + (size_t)(e / v4) * p.ld)[e % v4];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int e = e0 + k * NT;
+                if (e < total4) {
+                    const int i = e / v4, r4 = e % v4;
+                    if (p.clear) reinterpret_cast<float4*>(gg + (size_t)i * p.ld)[r4] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 o = reinterpret_cast<const float4*>(so + i * vP)[r4];
+                    const float rs = srs[i];
+                    store4<TO>(og + (size_t)i * p.H * dv + 4 * r4,
+                               (o.x * rs) * (g[k].x / (1.0f + expf(-g[k].x))), (o.y * rs) * (g[k].y / (1.0f + expf(-g[k].y))),
+                               (o.z * rs) * (g[k].z / (1.0f + expf(-g[k].z))), (o.w * rs) * (g[k].w / (1.0f + expf(-g[k].w))));
+                }
+            }
+        }
+        return;
+    }
     for (int i = warp; i < n; i += NT / 32) {                         // the rows' norms and gates: a warp per token
         float ss = 0.f;
         for (int r = lane; r < dv; r += 32) ss = fmaf(so[i * vP + r], so[i * vP + r], ss);
