@@ -28,6 +28,7 @@ class GroupSpec:
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2      # planes of a page: keys and values, or 1 for a cache of one vector per token
 
 
 class CacheAccountingError(RuntimeError):

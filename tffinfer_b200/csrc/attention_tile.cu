@@ -1,0 +1,241 @@
+// Softmax attention over the paged cache for tiles of packed query rows, computed in float32 with plain FMAs, for
+// the geometries and score rules the tensor-core kernels do not take:
+//
+// * keys of d and values of dv elements, any sizes (d, dv <= 1024 as far as shared memory reaches);
+// * values in a plane of their own (cache [pages, layers, 2, kv heads, page, slot]) or, in a cache of ONE plane
+//   ([pages, layers, 1, kv heads, page, slot]), the value of a token being the first dv elements of its key: a
+//   latent attention, where every query head reads the same small vector per token;
+// * visibility: causal, and optionally a sliding window (keys p-window+1 .. p) and/or blocks of ``chunk``
+//   positions counted from position 0 of the sequence (key n is seen from p only if n / chunk == p / chunk);
+// * score(p, n) = (q . k_n) * scale * temp[h]  -  r1[h] * ln(1 + r2[h] * (p - n)), with per-head float32 arrays temp
+//   (null: 1) and r1, r2 (null: no distance term);
+// * the output is multiplied by out_scale and may go to a column block of a wider row (out_ld, out_off).
+//
+// A tile is ROWS packed rows of one request and one key/value head: row r of the request is (token r / G, query head
+// r % G of the G heads that share the key/value head).  Key blocks of KB keys are aligned to absolute positions and a
+// row's running maximum and sum only ever see its own visible keys, so a row's result does not depend on the tile it
+// is in, on how the prompt was cut or on what else is in the batch.  Keys outside the tile's range are never read
+// (pages behind a window may have been given back).
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 32, KB = 32, THREADS = 256;
+
+struct TileArgs {
+    const int* q_start; const int* pos_start; const int* block_table; int table_width;
+    long long page_stride, head_stride, v_offset;   // elements; v_offset from a key's slot to the value's (0: the key itself)
+    int slot, page_size;
+    int nq, nkv, d, dv;
+    float scale; int window, chunk;
+    const float* temp; const float* r1; const float* r2;
+    float out_scale; int q_ld, out_ld, out_off;
+};
+
+template <typename TQ, typename TC, int NC>
+__global__ void __launch_bounds__(THREADS)
+attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ* __restrict__ out, TileArgs a) {
+    extern __shared__ float sm[];
+    const int d = a.d, dv = a.dv, G = a.nq / a.nkv;
+    const int kstride = d + 1;                                  // odd: lanes that read one column of 16 keys hit 16 banks
+    const bool own_v = a.v_offset != 0;
+    float* Qs = sm;                                             // [ROWS][d]
+    float* Ks = Qs + ROWS * d;                                  // [KB][d + 1]
+    float* Vs = Ks + KB * kstride;                              // [KB][dv] when values have a plane of their own
+    float* Ps = Vs + (own_v ? KB * dv : 0);                     // [ROWS][KB + 1]
+    float* alpha_s = Ps + ROWS * (KB + 1);                      // [ROWS]
+    int* row_p = (int*)(alpha_s + ROWS);                        // [ROWS] position, -1 = no such row
+    int* row_lo = row_p + ROWS;                                 // [ROWS] first visible key
+
+    pdl_launch_dependents();
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = a.q_start[b], q_len = a.q_start[b + 1] - t0, pos0 = a.pos_start[b];
+    const int n_rows = q_len * G, r0 = blockIdx.x * ROWS;
+    if (r0 >= n_rows) return;
+    pdl_wait();
+
+    if (tid < ROWS) {
+        const int r = r0 + tid;
+        int p = -1, lo = 0;
+        if (r < n_rows) {
+            p = pos0 + r / G;
+            if (a.window > 0) lo = max(lo, p - a.window + 1);
+            if (a.chunk > 0) lo = max(lo, (p / a.chunk) * a.chunk);
+        }
+        row_p[tid] = p; row_lo[tid] = lo;
+    }
+    for (int idx = tid; idx < ROWS * d; idx += THREADS) {
+        const int rr = idx / d, i = idx % d, r = r0 + rr;
+        float v = 0.f;
+        if (r < n_rows) v = to_f32<TQ>(q[(size_t)(t0 + r / G) * a.q_ld + (size_t)(kvh * G + r % G) * d + i]);
+        Qs[idx] = v;
+    }
+    __syncthreads();
+    const int last = min(r0 + ROWS, n_rows) - 1;
+    const int p_max = pos0 + last / G;
+    const int lo_min = row_lo[0];                               // positions rise with the row, and so do the lower ends
+
+    // score phase: thread -> rows 2*ry, 2*ry+1 and keys kx, kx+16;  value phase: the same rows, columns cx + 16*j
+    const int ry = tid >> 4, kx = tid & 15, cx = kx;
+    const int ra = 2 * ry, rb = 2 * ry + 1;
+    const int pa = row_p[ra], pb = row_p[rb], la = row_lo[ra], lb = row_lo[rb];
+    const int ha = kvh * G + (r0 + ra) % G, hb = kvh * G + (r0 + rb) % G;
+    const float sa = a.scale * (a.temp ? a.temp[ha] : 1.f), sb = a.scale * (a.temp ? a.temp[hb] : 1.f);
+    const bool biased = a.r1 != nullptr;
+    const float r1a = biased ? a.r1[ha] : 0.f, r2a = biased ? a.r2[ha] : 0.f;
+    const float r1b = biased ? a.r1[hb] : 0.f, r2b = biased ? a.r2[hb] : 0.f;
+    float oa[NC], ob[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) { oa[j] = 0.f; ob[j] = 0.f; }
+    // softmax phase: warp w owns rows 4w .. 4w+3, lane = key of the block
+    float m_run[4], l_run[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+    const int* table = a.block_table + (size_t)b * a.table_width;
+
+    for (int k0 = (lo_min / KB) * KB; k0 <= p_max; k0 += KB) {
+        // the block's keys (and values) into shared memory as float32; keys outside [lo_min, p_max] are zeros
+        for (int kk = warp; kk < KB; kk += THREADS / 32) {
+            const int n = k0 + kk;
+            const TC* src = nullptr;
+            if (n >= lo_min && n <= p_max) {
+                const int page = table[n / a.page_size];
+                if (page >= 0)
+                    src = cache + (size_t)page * a.page_stride + (size_t)kvh * a.head_stride + (size_t)(n % a.page_size) * a.slot;
+            }
+            for (int i = lane; i < d; i += 32) Ks[kk * kstride + i] = src ? to_f32<TC>(src[i]) : 0.f;
+            if (own_v)
+                for (int i = lane; i < dv; i += 32) Vs[kk * dv + i] = src ? to_f32<TC>(src[a.v_offset + i]) : 0.f;
+        }
+        __syncthreads();
+        {
+            float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
+            const float* qa = Qs + ra * d; const float* qb = Qs + rb * d;
+            const float* ka = Ks + kx * kstride; const float* kb = Ks + (kx + 16) * kstride;
+#pragma unroll 4
+            for (int i = 0; i < d; ++i) {
+                const float x0 = qa[i], x1 = qb[i], y0 = ka[i], y1 = kb[i];
+                s00 = fmaf(x0, y0, s00); s01 = fmaf(x0, y1, s01);
+                s10 = fmaf(x1, y0, s10); s11 = fmaf(x1, y1, s11);
+            }
+            const int n0 = k0 + kx, n1 = k0 + kx + 16;
+            auto score = [&](float dot, float sc, float r1, float r2, int p, int lo, int n) -> float {
+                if (p < 0 || n > p || n < lo) return -INFINITY;
+                float s = dot * sc;
+                if (biased) s -= r1 * log1pf(r2 * (float)(p - n));
+                return s;
+            };
+            Ps[ra * (KB + 1) + kx] = score(s00, sa, r1a, r2a, pa, la, n0);
+            Ps[ra * (KB + 1) + kx + 16] = score(s01, sa, r1a, r2a, pa, la, n1);
+            Ps[rb * (KB + 1) + kx] = score(s10, sb, r1b, r2b, pb, lb, n0);
+            Ps[rb * (KB + 1) + kx + 16] = score(s11, sb, r1b, r2b, pb, lb, n1);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = warp * 4 + i;
+            const float s = Ps[rr * (KB + 1) + lane];
+            const float m_new = fmaxf(m_run[i], warp_max(s));
+            float alpha = 1.f, pr = 0.f;
+            if (m_new != -INFINITY) {
+                alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
+                pr = expf(s - m_new);                           // -inf - finite = -inf -> 0
+            }
+            l_run[i] = l_run[i] * alpha + warp_sum(pr);
+            m_run[i] = m_new;
+            Ps[rr * (KB + 1) + lane] = pr;
+            if (lane == 0) alpha_s[rr] = alpha;
+        }
+        __syncthreads();
+        {
+            const float al_a = alpha_s[ra], al_b = alpha_s[rb];
+#pragma unroll
+            for (int j = 0; j < NC; ++j) { oa[j] *= al_a; ob[j] *= al_b; }
+            const float* vbase = own_v ? Vs : Ks;
+            const int vstride = own_v ? dv : kstride;
+            for (int kk = 0; kk < KB; ++kk) {
+                const float p0 = Ps[ra * (KB + 1) + kk], p1 = Ps[rb * (KB + 1) + kk];
+                const float* v = vbase + kk * vstride;
+#pragma unroll
+                for (int j = 0; j < NC; ++j) {
+                    const int c = cx + 16 * j;
+                    if (c < dv) {
+                        const float x = v[c];
+                        oa[j] = fmaf(p0, x, oa[j]); ob[j] = fmaf(p1, x, ob[j]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // the rows' sums live in the softmax warps: hand them over through shared memory
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (lane == 0) alpha_s[warp * 4 + i] = l_run[i];
+    __syncthreads();
+#pragma unroll
+    for (int side = 0; side < 2; ++side) {
+        const int rr = side ? rb : ra, r = r0 + rr;
+        if (r >= n_rows) continue;
+        const float inv = a.out_scale / alpha_s[rr];
+        TQ* orow = out + (size_t)(t0 + r / G) * a.out_ld + a.out_off + (size_t)(kvh * G + r % G) * dv;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+            const int c = cx + 16 * j;
+            if (c < dv) orow[c] = from_f32<TQ>((side ? ob[j] : oa[j]) * inv);
+        }
+    }
+}
+
+template <typename TQ, typename TC>
+int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, int num_requests, int max_q_len,
+                cudaStream_t stream) {
+    const int G = a.nq / a.nkv;
+    const int tiles = (max_q_len * G + ROWS - 1) / ROWS;
+    if (num_requests > 65535 || a.nkv > 65535) return TFF_ERR_UNSUPPORTED;
+    const bool own_v = a.v_offset != 0;
+    const size_t smem = sizeof(float) * ((size_t)ROWS * a.d + (size_t)KB * (a.d + 1) + (own_v ? (size_t)KB * a.dv : 0) +
+                                         (size_t)ROWS * (KB + 1) + ROWS) + sizeof(int) * 2 * ROWS;
+    if (smem > 220 * 1024) return TFF_ERR_UNSUPPORTED;
+    dim3 grid(tiles, a.nkv, num_requests);
+#define TFF_TILE(NCV)                                                                                                \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(attention_tile_kernel<TQ, TC, NCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tff_launch_pdl(attention_tile_kernel<TQ, TC, NCV>, grid, dim3(THREADS), smem, stream, (const TQ*)q,   \
+                              (const TC*)cache, (TQ*)out, a);                                                        \
+    } while (0)
+    if (a.dv <= 64) TFF_TILE(4);
+    if (a.dv <= 128) TFF_TILE(8);
+    if (a.dv <= 256) TFF_TILE(16);
+    if (a.dv <= 512) TFF_TILE(32);
+    if (a.dv <= 1024) TFF_TILE(64);
+#undef TFF_TILE
+    return TFF_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// q [tokens, q_ld] with head h at columns h*d; the cache pointer is the start of the layer's share of the pool (the
+// layer's offset already added); ``planes`` 2: values in the second plane of a page, 1: the value is the first dv
+// elements of the key's slot.  is_bf16: q, out and the cache are bfloat16, else float32.
+TFF_API int tff_attention_tile(
+    const void* q, int is_bf16, int q_ld, const int* q_start, const int* pos_start, const int* block_table,
+    int table_width, const void* cache, long long page_stride, int planes, int page_size, int slot,
+    void* out, int out_ld, int out_off, int num_requests, int max_q_len, int nq, int nkv, int d, int dv, float scale,
+    int window, int chunk, const float* temp, const float* r1, const float* r2, float out_scale, cudaStream_t stream) {
+    if (num_requests <= 0 || max_q_len <= 0) return TFF_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || dv <= 0 || slot < d || page_size <= 0 || window < 0 || chunk < 0 ||
+        (planes != 1 && planes != 2) || (planes == 2 && slot < dv) || (planes == 1 && dv > d) || ((r1 == nullptr) != (r2 == nullptr)))
+        return TFF_ERR_BAD_ARGUMENT;
+    TileArgs a;
+    a.q_start = q_start; a.pos_start = pos_start; a.block_table = block_table; a.table_width = table_width;
+    a.page_stride = page_stride; a.head_stride = (long long)page_size * slot;
+    a.v_offset = planes == 2 ? (long long)nkv * page_size * slot : 0;
+    a.slot = slot; a.page_size = page_size; a.nq = nq; a.nkv = nkv; a.d = d; a.dv = dv; a.scale = scale;
+    a.window = window; a.chunk = chunk; a.temp = temp; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
+    a.q_ld = q_ld; a.out_ld = out_ld; a.out_off = out_off;
+    if (is_bf16) return launch_tile<bf16, bf16>(q, cache, out, a, num_requests, max_q_len, stream);
+    return launch_tile<float, float>(q, cache, out, a, num_requests, max_q_len, stream);
+}

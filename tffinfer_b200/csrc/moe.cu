@@ -1,0 +1,166 @@
+// The small kernels around a routed feed-forward (mixture of experts); the experts' products are gemm_grouped.cu.
+//
+//   route    per token: z = W_r h in float32 (one warp per expert, a fixed order of additions), s = sigmoid(z), the
+//            ``top`` experts of largest s (the lower index wins a tie), optionally renormalised to sum 1; writes the
+//            pair (token, k) -> (expert, weight) and counts the pairs of every expert
+//   plan     one block: the experts' row ranges in the sorted order, the tile table of the grouped product (tiles of
+//            ``tile_rows`` rows that never span two experts), and the counters back to zero for the next call
+//   gather   per pair: its place among its expert's rows (an atomic cursor: the order within an expert is not fixed,
+//            but a row's result does not depend on its place), row_map[place] = pair, and the expert's input row
+//            x[place] = w * h[token] (weight on the input) or h[token]
+//   combine  per token: residual[t] += sum_k y[t * top + k] (times the weight when it multiplies the output), in
+//            the order k = 0 .. top-1
+#include "common.cuh"
+
+namespace {
+
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int W, int E, int top, int renormalize,
+                 int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ counts) {
+    extern __shared__ float sm[];              // W floats: the token's row; E floats: the scores
+    float* row = sm;
+    float* score = sm + W;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < W; i += 128) row[i] = to_f32<TH>(h[(size_t)t * W + i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += 4) {
+        const TW* wr = w_router + (size_t)e * W;
+        float acc = 0.f;
+        for (int i = lane; i < W; i += 32) acc = fmaf(row[i], to_f32<TW>(wr[i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-acc));
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -1.f; int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float s = score[e];
+            if (s > best) { best = s; arg = e; }      // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            pair_expert[(size_t)t * top + k] = arg;
+            pair_weight[(size_t)t * top + k] = best;
+            atomicAdd(&counts[arg], 1);
+            score[arg] = -2.f;                        // taken
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renormalize && lane == 0)
+        for (int k = 0; k < top; ++k) pair_weight[(size_t)t * top + k] /= total;
+}
+
+__global__ void moe_plan_kernel(int* __restrict__ counts, int E, int tile_rows, int* __restrict__ cursor,
+                                int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ tile_row_end,
+                                int* __restrict__ num_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    int off = 0, n = 0;
+    for (int e = 0; e < E; ++e) {
+        const int c = counts[e];
+        counts[e] = 0;
+        cursor[e] = off;
+        for (int r = off; r < off + c; r += tile_rows) { tile_group[n] = e; tile_row0[n] = r; tile_row_end[n] = off + c; ++n; }
+        off += c;
+    }
+    *num_tiles = n;
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restrict__ pair_expert,
+                  const float* __restrict__ pair_weight, int weight_on_input, int* __restrict__ cursor,
+                  int* __restrict__ row_map, TH* __restrict__ x) {
+    __shared__ int place_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pair = blockIdx.x;
+    if (threadIdx.x == 0) {
+        place_s = atomicAdd(&cursor[pair_expert[pair]], 1);
+        row_map[place_s] = pair;
+    }
+    __syncthreads();
+    const int place = place_s;
+    const float w = weight_on_input ? pair_weight[pair] : 1.f;
+    const TH* src = h + (size_t)(pair / top) * W;
+    TH* dst = x + (size_t)place * W;
+    for (int i = threadIdx.x; i < W; i += 128) dst[i] = from_f32<TH>(w * to_f32<TH>(src[i]));
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __restrict__ pair_weight,
+                   int weight_on_output, float* __restrict__ residual, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int i = blockIdx.y * 256 + threadIdx.x;
+    if (i >= W) return;
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const float w = weight_on_output ? pair_weight[(size_t)t * top + k] : 1.f;
+        acc = fmaf(w, y[((size_t)t * top + k) * W + i], acc);
+    }
+    const size_t at = (size_t)t * W + i;
+    out[at] = residual ? residual[at] + acc : acc;
+}
+
+}  // namespace
+
+TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
+                          int renormalize, int* pair_expert, float* pair_weight, int* counts, cudaStream_t stream) {
+    if (T <= 0) return TFF_OK;
+    if (W <= 0 || E <= 0 || top <= 0 || top > E || !h || !w_router) return TFF_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(W + E) * sizeof(float);
+    if (smem > 200 * 1024) return TFF_ERR_UNSUPPORTED;
+#define TFF_ROUTE(TH, TW)                                                                                             \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(moe_route_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        return tff_launch_pdl(moe_route_kernel<TH, TW>, dim3(T), dim3(128), smem, stream, (const TH*)h,               \
+                              (const TW*)w_router, W, E, top, renormalize, pair_expert, pair_weight, counts);         \
+    } while (0)
+    if (h_dt == 0 && w_dt == 0) TFF_ROUTE(float, float);
+    if (h_dt == 0 && w_dt == 1) TFF_ROUTE(float, bf16);
+    if (h_dt == 1 && w_dt == 1) TFF_ROUTE(bf16, bf16);
+    if (h_dt == 1 && w_dt == 0) TFF_ROUTE(bf16, float);
+#undef TFF_ROUTE
+    return TFF_ERR_BAD_ARGUMENT;
+}
+
+TFF_API int tff_moe_plan(int* counts, int E, int tile_rows, int* cursor, int* tile_group, int* tile_row0,
+                         int* tile_row_end, int* num_tiles, cudaStream_t stream) {
+    if (E <= 0 || tile_rows <= 0) return TFF_ERR_BAD_ARGUMENT;
+    return tff_launch_pdl(moe_plan_kernel, dim3(1), dim3(32), 0, stream, counts, E, tile_rows, cursor, tile_group,
+                          tile_row0, tile_row_end, num_tiles);
+}
+
+TFF_API int tff_moe_gather(const void* h, int h_dt, int pairs, int W, int top, const int* pair_expert,
+                           const float* pair_weight, int weight_on_input, int* cursor, int* row_map, void* x,
+                           cudaStream_t stream) {
+    if (pairs <= 0) return TFF_OK;
+    if (h_dt == 0)
+        return tff_launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (const float*)h, W, top,
+                              pair_expert, pair_weight, weight_on_input, cursor, row_map, (float*)x);
+    return tff_launch_pdl(moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (const bf16*)h, W, top,
+                          pair_expert, pair_weight, weight_on_input, cursor, row_map, (bf16*)x);
+}
+
+TFF_API int tff_moe_combine(const float* y, int T, int W, int top, const float* pair_weight, int weight_on_output,
+                            float* residual, float* out, cudaStream_t stream) {
+    if (T <= 0) return TFF_OK;
+    dim3 grid(T, (W + 255) / 256);
+    return tff_launch_pdl(moe_combine_kernel, grid, dim3(256), 0, stream, y, W, top, pair_weight, weight_on_output,
+                          residual, out);
+}

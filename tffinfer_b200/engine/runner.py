@@ -91,29 +91,31 @@ class ModelRunner:
         self.bindings: List[CacheBinding] = [CacheBinding() for _ in needs]
         state_specs = []
         for e, need in enumerate(needs):
-            if isinstance(need, KVNeed):
-                key = (need.num_kv_heads, need.head_dim, need.window)
-                for g, spec in enumerate(groups):
-                    if (spec.num_kv_heads, spec.head_dim, spec.window) == key:
-                        break
-                else:
-                    groups.append(GroupSpec(0, need.num_kv_heads, need.head_dim, need.window))
-                    members.append([])
-                    g = len(groups) - 1
-                self.bindings[e] = CacheBinding(group=g, layer_in_group=len(members[g]), write=True)
-                members[g].append(e)
-            elif isinstance(need, StateNeed):
-                self.bindings[e] = CacheBinding(state_index=len(state_specs))
-                state_specs.append(need)
+            # a mixer may keep pages, a state, or both (a tuple): the binding carries a group and a state index
+            for one in (need if isinstance(need, (tuple, list)) else (need,)):
+                if isinstance(one, KVNeed):
+                    key = (one.num_kv_heads, one.head_dim, one.window, one.planes)
+                    for g, spec in enumerate(groups):
+                        if (spec.num_kv_heads, spec.head_dim, spec.window, spec.planes) == key:
+                            break
+                    else:
+                        groups.append(GroupSpec(0, one.num_kv_heads, one.head_dim, one.window, one.planes))
+                        members.append([])
+                        g = len(groups) - 1
+                    self.bindings[e].group, self.bindings[e].layer_in_group, self.bindings[e].write = g, len(members[g]), True
+                    members[g].append(e)
+                elif isinstance(one, StateNeed):
+                    self.bindings[e].state_index = len(state_specs)
+                    state_specs.append(one)
         for e, entry in enumerate(self.desc.schedule):
             if entry.cache_of is not None:
                 src = self.bindings[entry.cache_of]
                 self.bindings[e] = CacheBinding(group=src.group, layer_in_group=src.layer_in_group,
                                                 write=False, state_index=src.state_index)
-        groups = [GroupSpec(len(m), s.num_kv_heads, s.head_dim, s.window) for s, m in zip(groups, members)]
+        groups = [GroupSpec(len(m), s.num_kv_heads, s.head_dim, s.window, s.planes) for s, m in zip(groups, members)]
         ps = self.ecfg.page_size
         elt = torch.empty((), dtype=self.act_dtype).element_size()
-        page_bytes = [g.num_layers * 2 * g.num_kv_heads * ps * g.head_dim * elt for g in groups]
+        page_bytes = [g.num_layers * g.planes * g.num_kv_heads * ps * g.head_dim * elt for g in groups]
         if self.ecfg.max_cache_tokens is not None:
             n_pages = [max(1, -(-self.ecfg.max_cache_tokens // ps)) for _ in groups]
         elif groups:
@@ -129,12 +131,12 @@ class ModelRunner:
             n_pages = []
         # one page and one state slot more than the pools hand out: padding rows of a
         # fixed-size batch write there and nobody reads them
-        # [pages, layers, 2, kv heads, page, head] as the parts and kernels index it, stored with the layers
+        # [pages, layers, planes, kv heads, page, head] as the parts and kernels index it, stored with the layers
         # outermost: the pages that one layer's attention reads then lie within that layer's share of the
         # pool (with the pages outermost they were 64 KB out of every layers x 64 KB, each in another 2 MB
         # page of the address space, and the attention of a 40-layer model read a quarter slower for it)
         self.kv_caches = [
-            torch.zeros((g.num_layers, n + 1, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype,
+            torch.zeros((g.num_layers, n + 1, g.planes, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype,
                         device=self.device).permute(1, 0, 2, 3, 4, 5)
             for n, g in zip(n_pages, groups)]
         self.dummy_pages = list(n_pages)

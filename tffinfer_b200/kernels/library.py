@@ -102,6 +102,7 @@ class CudaKernels:
         self._accumulators = {}    # (shape, device) -> float32 buffer kept at zero between uses
         self._acc_zero = {}        # data_ptr -> True while the buffer is known to hold zeros
         self._inv_freq_cache = {}
+        self._moe_counts = {}      # (experts, device) -> int32 counters that the routed feed-forward keeps at zero
         # the planners below cut work by the SM count the launchers size their grids with
         self.NUM_SMS = int(self.lib.tff_sm_count())
         if self.NUM_SMS <= 0:
@@ -394,6 +395,8 @@ class CudaKernels:
         for buf in self._accumulators.values():
             buf.zero_()
             self._acc_zero[buf.data_ptr()] = True
+        for counts in self._moe_counts.values():
+            counts.zero_()
 
     # ------------------------------------------------------- folded decode products
     def can_fold_norm(self, x, weight, out_dtype) -> bool:
@@ -518,13 +521,13 @@ class CudaKernels:
     # ------------------------------------------------------- mixers with a rotation computed on the fly
     def qkv_finish(self, proj, q_out, k_out, freq, batch, block_table, kv_cache, kv_layer, page_size, nq, nkv, d, dv,
                    k_scale: float = 1.0, v_mode: int = 0, v_share=None, lam=None, gate_off: int = -1, gate_out=None,
-                   last_reader: bool = True) -> None:
+                   last_reader: bool = True, proj_off: int = 0) -> None:
         """proj [T, ld] = [q (nq*d) | k (nkv*d) | v (nkv*dv) | ...] -> rotated q in ``q_out`` [T, nq*d]; rotated k
         (times ``k_scale``) and v into the tokens' cache slots or, with no cache, k into ``k_out`` (float32);
         ``freq`` = (frequencies, rot_dim, magnitude, interleaved) or None; value mixing and head gates as
         csrc/qkv_finish.cu describes them.  When ``proj`` is one of the accumulator buffers that are kept at zero
         between uses, what the kernel consumes is set back to zero; ``last_reader`` says that nothing of the row is
-        left for another kernel (which then clears the rest)."""
+        left for another kernel (which then clears the rest).  ``proj_off``: the row's q starts at that column."""
         self._need_cuda(proj, q_out, k_out, block_table, v_share, lam, gate_out)
         T, ld = proj.shape
         f, rot, mag, inter = freq if freq is not None else (None, 0, 1.0, False)
@@ -534,7 +537,8 @@ class CudaKernels:
             assert tuple(kv_cache.shape[2:5]) == (2, nkv, page_size)
         clear = 1 if proj.data_ptr() in self._acc_zero else 0
         self._check(self.lib.tff_qkv_finish(
-            _ptr(proj), _c_int(_dt(proj)), _c_int(clear), _c_int(ld), _ptr(q_out), _c_int(_dt(q_out)), _ptr(k_out),
+            _vp(proj.data_ptr() + proj_off * proj.element_size()), _c_int(_dt(proj)), _c_int(clear), _c_int(ld), _ptr(q_out),
+            _c_int(_dt(q_out)), _ptr(k_out),
             _ptr(f), _c_int(rot), _c_float(mag), _c_int(1 if inter else 0), _c_float(k_scale),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
@@ -641,6 +645,187 @@ class CudaKernels:
         if clear:
             self._acc_zero[vg.data_ptr()] = True
         self.launches += kernels
+
+    # ------------------------------------------------------- attention in float32 tiles (any sizes, latent caches, biases)
+    @staticmethod
+    def _layer_cache(kv_cache, kv_layer: int):
+        """(pointer to the layer's share of the pool, elements between its pages) of a cache
+        [pages, layers, planes, kv heads, page, slot], stored with the pages or with the layers outermost."""
+        if not kv_cache.is_cuda:
+            raise KernelError("a tensor given to a CUDA kernel is not on a CUDA device")
+        st, block = kv_cache.stride(), 1
+        for i in range(kv_cache.dim() - 1, 1, -1):
+            if st[i] != block:
+                raise KernelError("the [planes, kv heads, page, slot] block of a cache page must be dense")
+            block *= kv_cache.shape[i]
+        return _vp(kv_cache.data_ptr() + kv_layer * st[1] * kv_cache.element_size()), st[0]
+
+    def attention_tile(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
+                       window: int = 0, chunk: int = 0, temp=None, r1=None, r2=None, out_scale: float = 1.0,
+                       out_off: int = 0) -> None:
+        """q [T, nq*d] against the paged cache -> columns out_off .. out_off + nq*dv of ``out`` (times out_scale), in
+        float32 arithmetic whatever the storage type.  The cache has two planes (keys, values) or one (the value
+        of a token is the first dv elements of its key).  Visibility: causal, within ``window`` keys, within the
+        query's block of ``chunk`` positions.  Scores: (q . k) * scale * temp[h] - r1[h] * ln(1 + r2[h] * distance)
+        (temp, r1, r2 float32 [nq] or None)."""
+        self._need_cuda(q, block_table, out, temp, r1, r2)
+        T = q.shape[0]
+        planes, slot = kv_cache.shape[2], kv_cache.shape[-1]
+        assert kv_cache.dtype == q.dtype == out.dtype and q.shape[1] == nq * d
+        assert tuple(kv_cache.shape[3:5]) == (nkv, page_size) and out.shape[0] == T and out.shape[1] >= out_off + nq * dv
+        for v in (temp, r1, r2):
+            assert v is None or (v.dtype == torch.float32 and v.numel() == nq)
+        c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
+        self._check(self.lib.tff_attention_tile(
+            _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(block_table),
+            _c_int(block_table.shape[1]), c_ptr, ctypes.c_longlong(page_stride), _c_int(planes), _c_int(page_size),
+            _c_int(slot), _ptr(out), _c_int(out.shape[1]), _c_int(out_off), _c_int(batch.num_requests),
+            _c_int(batch.max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_float(scale), _c_int(window),
+            _c_int(chunk), _ptr(temp), _ptr(r1), _ptr(r2), _c_float(out_scale), self._stream()), "attention_tile")
+        self.launches += 1
+
+    # ------------------------------------------------------- many small products in one launch
+    def gemm_grouped(self, a, b, c, groups: int, M: int, N: int, K: int, lda: int, a_gs: int, ldb: int, b_gs: int,
+                     ldc: int, c_gs: int, b2=None, activation: str = "silu", tiles=None, row_map=None) -> None:
+        """c_g = a_g @ b_g^T for ``groups`` groups whose operands lie a_gs, b_gs, c_gs elements apart (rows lda, ldb,
+        ldc elements apart), in float32 FMAs with a fixed order of additions.  With ``b2``: act(a b^T) * (a b2^T).
+        ``tiles`` = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles) is the ragged form (rows of ``a`` sorted
+        by group, the table on the device); ``row_map`` sends product row r to row row_map[r] of ``c``."""
+        self._need_cuda(a, b, c, b2, row_map)
+        assert b2 is None or b2.dtype == b.dtype
+        tg = tr0 = tre = nt = None
+        max_tiles = 0
+        if tiles is not None:
+            tg, tr0, tre, nt, max_tiles = tiles
+        self._check(self.lib.tff_gemm_grouped(
+            _ptr(a), _c_int(_dt(a)), ctypes.c_longlong(lda), ctypes.c_longlong(a_gs),
+            _ptr(b), _ptr(b2), _c_int(_dt(b)), ctypes.c_longlong(ldb), ctypes.c_longlong(b_gs),
+            _ptr(c), _c_int(_dt(c)), ctypes.c_longlong(ldc), ctypes.c_longlong(c_gs),
+            _ptr(tg), _ptr(tr0), _ptr(tre), _ptr(nt), _c_int(max_tiles), _ptr(row_map),
+            _c_int(groups), _c_int(M), _c_int(N), _c_int(K), _c_int(self.ACTIVATION_CODES[activation]),
+            self._stream()), "gemm_grouped")
+        self.launches += 1
+
+    # ------------------------------------------------------- routed feed-forward (mixture of experts)
+    def routed_mlp(self, h, w_router, w_gate, w_up, w_down, residual, top: int, renormalize: bool = False,
+                   weight_on: str = "output", activation: str = "silu", out=None) -> None:
+        """residual += sum over a token's ``top`` experts of down_e(act(gate_e(x)) * up_e(x)), the experts chosen by
+        the largest sigmoid(W_r h) (computed in float32), weights the scores themselves or renormalised to sum 1;
+        ``weight_on`` "input": x = w h and the outputs are summed as they are; "output": x = h and the outputs are
+        summed with the weights.  w_gate, w_up [E, ff, W], w_down [E, W, ff].  With ``residual`` None the sum goes to
+        ``out``.  Six launches, no host synchronisation: route, plan, gather, two grouped products over the tokens
+        sorted by expert, combine (a token's experts are added in the order of their rank)."""
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
+        self._need_cuda(h, w_router, w_gate, w_up, w_down, residual, out)
+        T, W = h.shape
+        E, ff = w_gate.shape[0], w_gate.shape[1]
+        assert tuple(w_router.shape) == (E, W) and tuple(w_up.shape) == (E, ff, W) and tuple(w_down.shape) == (E, W, ff)
+        assert weight_on in ("input", "output") and 0 < top <= E
+        target = residual if residual is not None else out
+        assert target.dtype == torch.float32 and tuple(target.shape) == (T, W)
+        dev, P = h.device, T * top
+        counts = self._moe_counts.get((E, str(dev)))
+        if counts is None:
+            counts = torch.zeros(E, dtype=torch.int32, device=dev)       # set back to zero by the plan kernel
+            self._moe_counts[(E, str(dev))] = counts
+        bm = int(self.lib.tff_gemm_grouped_tile_rows())
+        max_tiles = -(-P // bm) + E
+        ints = torch.empty(2 * P + E + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
+        pair_expert, row_map, cursor = ints[:P], ints[P:2 * P], ints[2 * P:2 * P + E]
+        o = 2 * P + E
+        tile_group, tile_row0, tile_row_end = ints[o:o + max_tiles], ints[o + max_tiles:o + 2 * max_tiles], ints[o + 2 * max_tiles:o + 3 * max_tiles]
+        num_tiles = ints[o + 3 * max_tiles:]
+        pair_weight = torch.empty(P, dtype=torch.float32, device=dev)
+        self._check(self.lib.tff_moe_route(_ptr(h), _c_int(_dt(h)), _ptr(w_router), _c_int(_dt(w_router)), _c_int(T), _c_int(W),
+                                           _c_int(E), _c_int(top), _c_int(1 if renormalize else 0), _ptr(pair_expert),
+                                           _ptr(pair_weight), _ptr(counts), self._stream()), "moe_route")
+        self._check(self.lib.tff_moe_plan(_ptr(counts), _c_int(E), _c_int(bm), _ptr(cursor), _ptr(tile_group), _ptr(tile_row0),
+                                          _ptr(tile_row_end), _ptr(num_tiles), self._stream()), "moe_plan")
+        x = torch.empty((P, W), dtype=h.dtype, device=dev)
+        self._check(self.lib.tff_moe_gather(_ptr(h), _c_int(_dt(h)), _c_int(P), _c_int(W), _c_int(top), _ptr(pair_expert),
+                                            _ptr(pair_weight), _c_int(1 if weight_on == "input" else 0), _ptr(cursor),
+                                            _ptr(row_map), _ptr(x), self._stream()), "moe_gather")
+        self.launches += 3
+        tiles = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles)
+        act = torch.empty((P, ff), dtype=h.dtype, device=dev)
+        self.gemm_grouped(x, w_gate, act, E, 0, ff, W, W, 0, W, ff * W, ff, 0, b2=w_up, activation=activation, tiles=tiles)
+        y = torch.empty((P, W), dtype=torch.float32, device=dev)
+        self.gemm_grouped(act, w_down, y, E, 0, W, ff, ff, 0, ff, W * ff, W, 0, tiles=tiles, row_map=row_map)
+        self._check(self.lib.tff_moe_combine(_ptr(y), _c_int(T), _c_int(W), _c_int(top), _ptr(pair_weight),
+                                             _c_int(1 if weight_on == "output" else 0), _ptr(residual), _ptr(target),
+                                             self._stream()), "moe_combine")
+        self.launches += 1
+
+    # ------------------------------------------------------- gated recurrence over a state of one vector
+    def min_gru(self, proj, z_off: int, x_off: int, g_off: int, bz, bx, state, batch, out, width: int, out_off: int = 0,
+                out_scale: float = 1.0, last_reader: bool = True) -> None:
+        """The minGRU recurrence (csrc/mingru.cu) from columns z_off.., x_off.., g_off.. of the float32 rows ``proj``
+        over ``state`` [slots, width] -> columns out_off .. out_off + width of ``out`` (times out_scale)."""
+        self._need_cuda(proj, bz, bx, state, out)
+        assert proj.dtype == torch.float32 and state.dtype == torch.float32 and state.shape[1] == width
+        assert out.shape[0] == proj.shape[0] and out.shape[1] >= out_off + width
+        for v in (bz, bx):
+            assert v is None or (v.dtype == torch.float32 and v.numel() == width)
+        clear = 1 if proj.data_ptr() in self._acc_zero else 0
+        self._check(self.lib.tff_min_gru(_ptr(proj), _c_int(proj.shape[1]), _c_int(z_off), _c_int(x_off), _c_int(g_off),
+                                         _c_int(clear), _ptr(bz), _ptr(bx), _ptr(state), _c_int(state.shape[0]),
+                                         _ptr(batch.q_start), _ptr(batch.slots), _c_int(batch.num_requests), _c_int(width),
+                                         _ptr(out), _c_int(_dt(out)), _c_int(out.shape[1]), _c_int(out_off),
+                                         _c_float(out_scale), self._stream()), "min_gru")
+        if clear and last_reader:
+            self._acc_zero[proj.data_ptr()] = True
+        self.launches += 1
+
+    # ------------------------------------------------------- latent attention
+    def latent_attend(self, h, w_down, q_norm_w, kv_norm_w, eps: float, w_uq, w_uk_t, w_uv, freq, batch, block_table,
+                      kv_cache, kv_layer, page_size, out, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int,
+                      kv_rank: int, scale: float, write_cache: bool) -> None:
+        """The whole of a latent attention between its input rows and its output projection -> out [T, heads*vdim].
+        ``w_down`` rows [query latent (q_rank) | kv latent (kv_rank) | shared rotated key part (rot_dim)], the last two
+        absent when the layer reads another layer's cache (``write_cache`` False).  The cache has one plane with a slot
+        [c | r] of kv_rank + rot_dim elements per token.  Per-head keys W_uk c are never made: the query's unrotated
+        part goes through W_uk^T instead (``w_uk_t`` [heads, kv_rank, dim]), attention then runs with one shared
+        key/value head over the slots (keys the whole slot, values its first kv_rank elements), and W_uv [heads*vdim,
+        kv_rank] takes every head's mixed latent to its value size."""
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
+        T = h.shape[0]
+        dev, dt = h.device, h.dtype
+        slot = kv_rank + rot_dim
+        assert kv_cache is not None and kv_cache.shape[2] == 1 and kv_cache.shape[3] == 1 and kv_cache.shape[-1] == slot
+        assert w_down.shape[0] >= (q_rank + slot if write_cache else q_rank)      # rows beyond are padding
+        f, rot_dims, mag, inter = freq if freq is not None else (None, 0, 1.0, True)
+        if rot_dims and (not inter or mag != 1.0):
+            raise KernelError("latent attention turns interleaved pairs by plain angles")
+        proj = self.projection_buffer(T, w_down.shape[0], dev, dt)
+        self.gemm(h, w_down, proj)
+        cq = torch.empty((T, q_rank), dtype=dt, device=dev)
+        c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
+        clear = 1 if proj.data_ptr() in self._acc_zero else 0
+        self._need_cuda(q_norm_w, kv_norm_w, f, block_table)
+        self._check(self.lib.tff_latent_finish(
+            _ptr(proj), _c_int(proj.shape[1]), _c_int(clear), _c_int(q_rank), _c_int(kv_rank if write_cache else 0),
+            _c_int(rot_dim), _c_int(rot_dims), _ptr(q_norm_w), _ptr(kv_norm_w), _c_float(eps), _ptr(f),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
+            c_ptr if write_cache else _vp(0), ctypes.c_longlong(page_stride), _c_int(page_size), _c_int(slot), _ptr(cq),
+            _c_int(_dt(cq)), _c_int(T), self._stream()), "latent_finish")
+        if clear:
+            self._acc_zero[proj.data_ptr()] = True
+        self.launches += 1
+        q = torch.empty((T, heads * (dim + rot_dim)), dtype=torch.float32, device=dev)
+        self.gemm(cq, w_uq, q)
+        q_lat = torch.empty((T, heads * slot), dtype=dt, device=dev)
+        self.gemm_grouped(q, w_uk_t, q_lat, heads, T, kv_rank, dim, heads * (dim + rot_dim), dim + rot_dim,
+                          dim, kv_rank * dim, heads * slot, slot)
+        self._check(self.lib.tff_latent_q_rot(_ptr(q), _c_int(dim), _c_int(rot_dim), _c_int(rot_dims), _ptr(f),
+                                              _ptr(batch.positions), _ptr(q_lat), _c_int(_dt(q_lat)), _c_int(kv_rank),
+                                              _c_int(heads), _c_int(T), self._stream()), "latent_q_rot")
+        self.launches += 1
+        o_lat = torch.empty((T, heads * kv_rank), dtype=dt, device=dev)
+        self.attention_tile(q_lat, batch, block_table, kv_cache, kv_layer, page_size, o_lat, heads, 1, slot, kv_rank, scale)
+        self.gemm_grouped(o_lat, w_uv, out, heads, T, vdim, kv_rank, heads * kv_rank, kv_rank, kv_rank, vdim * kv_rank,
+                          heads * vdim, vdim)
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
         """table float32 [max_pos, rot_dim/2, 2] = (cos, sin)(pos * theta^(-2i/rot_dim)).

@@ -19,7 +19,7 @@ from typing import Dict, Optional
 import torch
 
 from ..registry import register_part
-from .base import Mixer, WeightSpec, MATRIX, VECTOR, KVNeed, LayerContext
+from .base import Mixer, SplitMixer, WeightSpec, MATRIX, VECTOR, KVNeed, LayerContext
 
 
 @register_part("mixer", "gqa_attention")
@@ -183,3 +183,87 @@ class GatedSinkAttention(Mixer):
             return out
         ops.gemm(attn, self.w_o, residual, residual=residual)
         return residual
+
+
+@register_part("mixer", "biased_chunk_attention")
+class BiasedChunkAttention(SplitMixer):
+    """Grouped-query softmax attention without a rotation, whose scores carry the positions:
+
+        score(p, n) = (q_p . k_n) * softmax_scale * temp_h  -  r1_h * ln(1 + r2_h * (p - n))
+
+    with learned per-head numbers temp (``head_temperature``) and r1, r2 (``distance_bias``), and whose visibility is
+    causal within blocks of ``chunk`` positions counted from position 0 of the sequence (key n is seen from p only if
+    n // chunk == p // chunk; 0 = no blocks) and/or within a sliding ``window``.  Keys of ``head_dim`` and values of
+    ``v_head_dim`` elements.  Everything behind the projections is float32 arithmetic (kernels/library.py
+    ``attention_tile``).  The cache keeps what a later query can still see: the last ``chunk`` (or ``window``) tokens."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int = 0,
+                 softmax_scale: Optional[float] = None, chunk: int = 0, window: int = 0, head_temperature: bool = False,
+                 distance_bias: bool = False, names: Optional[Dict[str, str]] = None, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.v_head_dim = int(v_head_dim) if v_head_dim else int(head_dim)
+        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.chunk, self.window = int(chunk), int(window)
+        self.head_temperature, self.distance_bias = bool(head_temperature), bool(distance_bias)
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.chunk < 0 or self.window < 0:
+            raise ValueError("chunk and window must not be negative")
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "temp": "temp", "r1": "r1", "r2": "r2"}
+        self.names.update(names or {})
+        self.q_width = self.num_heads * self.head_dim
+        self.k_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_kv_heads * self.v_head_dim
+        self.cache_dim = max(self.head_dim, self.v_head_dim)     # a cache slot holds a key or a value
+        self.w_in = self.w_o = self.temp = self.r1 = self.r2 = None
+
+    def cache_need(self):
+        spans = [s for s in (self.chunk, self.window) if s > 0]
+        return KVNeed(self.num_kv_heads, self.cache_dim, min(spans) if spans else 0)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n = self.names
+        s = {n["q"]: WeightSpec((self.q_width, self.hidden_size), MATRIX),
+             n["k"]: WeightSpec((self.k_width, self.hidden_size), MATRIX),
+             n["v"]: WeightSpec((self.v_width, self.hidden_size), MATRIX),
+             n["o"]: WeightSpec((self.hidden_size, self.num_heads * self.v_head_dim), MATRIX)}
+        if self.head_temperature:
+            s[n["temp"]] = WeightSpec((self.num_heads,), VECTOR, init="one_plus_normal", init_scale=0.2)
+        if self.distance_bias:
+            s[n["r1"]] = WeightSpec((self.num_heads,), VECTOR, init="one_plus_normal", init_scale=0.2)
+            s[n["r2"]] = WeightSpec((self.num_heads,), VECTOR, init="one_plus_normal", init_scale=0.2)
+        return s
+
+    def load(self, tensors, ops, act_dtype) -> None:
+        n = self.names
+        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        dt = rows[0].dtype if all(r.dtype == rows[0].dtype for r in rows) else torch.float32
+        self.w_in = torch.cat([r.to(dt) for r in rows], dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        self.temp = tensors[n["temp"]].contiguous() if self.head_temperature else None
+        self.r1 = tensors[n["r1"]].contiguous() if self.distance_bias else None
+        self.r2 = tensors[n["r2"]].contiguous() if self.distance_bias else None
+
+    def input_rows(self):
+        return self.w_in
+
+    def mixed_width(self) -> int:
+        return self.num_heads * self.v_head_dim
+
+    def output_cols(self):
+        return self.w_o
+
+    def mix(self, proj, col, ctx: LayerContext, mixed, mixed_col, out_scale, last_reader) -> None:
+        if not ctx.write_cache:
+            raise ValueError("biased_chunk_attention writes the keys and values it attends to; a borrowed cache is not supported")
+        ops, batch = ctx.ops, ctx.batch
+        q = torch.empty((proj.shape[0], self.q_width), dtype=mixed.dtype, device=mixed.device)
+        ops.qkv_finish(proj, q, None, None, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
+                       self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, last_reader=last_reader,
+                       proj_off=col)
+        ops.attention_tile(q, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, mixed, self.num_heads,
+                           self.num_kv_heads, self.head_dim, self.v_head_dim, self.scale, window=self.window,
+                           chunk=self.chunk, temp=self.temp, r1=self.r1, r2=self.r2, out_scale=out_scale,
+                           out_off=mixed_col)

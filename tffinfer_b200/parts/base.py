@@ -30,10 +30,13 @@ class WeightSpec:
 # --- cache needs ---------------------------------------------------------------
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values of every token (window == 0) or of the last ``window`` tokens."""
+    """Keys and values of every token (window == 0) or of the last ``window`` tokens.  ``planes`` 2: a page holds a
+    plane of keys and a plane of values, slots of ``head_dim`` elements each; 1: one plane, a token's slot is one
+    vector of ``head_dim`` elements from which the mixer makes both (a latent cache)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -123,7 +126,8 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """Mixes information between the tokens of a request (attention here).
 
-    cache_need() -> KVNeed | StateNeed | None
+    cache_need() -> KVNeed | StateNeed | None, or a tuple (KVNeed, StateNeed) for a mixer that keeps both (two
+    mixers side by side): the layer context then carries pages and a state
     forward(h, ctx, residual) -> float32 [T, hidden]: residual + mixer(h); with ``residual`` None, mixer(h)
     alone in a tensor of its own (arrangements that do something else with it than add it to one stream).
     """
@@ -132,6 +136,58 @@ class Mixer(Part):
 
     def forward(self, h: torch.Tensor, ctx: LayerContext, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+
+class SplitMixer(Mixer):
+    """A mixer of the shape  input projection -> token mixing -> output projection  that lets somebody else run the
+    two projections: several such mixers side by side then share ONE input product and ONE output product
+    (parts/parallel.py).  After ``load``:
+
+    input_rows()    the rows of its input projection [n_in, hidden] (its columns of the shared product, in its order)
+    mixed_width()   how many columns its mixed activation has
+    output_cols()   its output projection [hidden, mixed_width]
+    mix(proj, col, ctx, mixed, mixed_col, out_scale, last_reader)
+                    reads columns col .. col + n_in of the float32 rows ``proj`` (the product's accumulators) and writes
+                    ``out_scale`` times its mixed activation into columns mixed_col .. of ``mixed`` (activation type).
+                    ``last_reader``: nothing of the rows is left for anybody else (accumulator buffers that are kept at
+                    zero between uses count as clean again).
+
+    ``forward`` runs the same three steps alone."""
+    def input_rows(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def mixed_width(self) -> int:
+        raise NotImplementedError
+
+    def output_cols(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def mix(self, proj, col: int, ctx: LayerContext, mixed, mixed_col: int, out_scale: float, last_reader: bool) -> None:
+        raise NotImplementedError
+
+    @staticmethod
+    def padded_rows(w: torch.Tensor) -> torch.Tensor:
+        pad = (-w.shape[0]) % 8               # a product's output rows are stored 16 bytes at a time
+        if pad:
+            w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
+        return w.contiguous()
+
+    def forward(self, h, ctx: LayerContext, residual):
+        ops = ctx.ops
+        T = h.shape[0]
+        w_in = getattr(self, "_w_in_alone", None)
+        if w_in is None:
+            w_in = self._w_in_alone = self.padded_rows(self.input_rows())
+        proj = ops.projection_buffer(T, w_in.shape[0], h.device, h.dtype)
+        ops.gemm(h, w_in, proj)
+        mixed = torch.empty((T, self.mixed_width()), dtype=h.dtype, device=h.device)
+        self.mix(proj, 0, ctx, mixed, 0, 1.0, True)
+        if residual is None:
+            out = ops.sublayer_output(T, self.output_cols().shape[0], h.device, h.dtype)
+            ops.gemm(mixed, self.output_cols(), out)
+            return out
+        ops.gemm(mixed, self.output_cols(), residual, residual=residual)
+        return residual
 
 
 class FeedForward(Part):

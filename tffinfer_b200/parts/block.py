@@ -11,8 +11,8 @@ from .base import Block, LayerContext
 class PreNormBlock(Block):
     def __init__(self, mixer, feed_forward, mixer_norm=None, ffn_norm=None, extra_norms=None):
         super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, extra_norms)
-        if mixer_norm is None or ffn_norm is None:
-            raise ValueError("the pre_norm arrangement needs mixer_norm and ffn_norm")
+        if mixer_norm is None or (ffn_norm is None and feed_forward is not None):
+            raise ValueError("the pre_norm arrangement needs mixer_norm, and ffn_norm where there is a feed-forward")
 
     @staticmethod
     def _normed(norm, consumer, x, ctx: LayerContext, act_dtype):
@@ -28,6 +28,8 @@ class PreNormBlock(Block):
     def forward(self, x, ctx: LayerContext, act_dtype):
         h = self._normed(self.mixer_norm, self.mixer, x, ctx, act_dtype)
         x = self.mixer.forward(h, ctx, residual=x)
+        if self.feed_forward is None:         # a layer of a mixer alone
+            return x
         h = self._normed(self.ffn_norm, self.feed_forward, x, ctx, act_dtype)
         x = self.feed_forward.forward(h, ctx, residual=x)
         return x

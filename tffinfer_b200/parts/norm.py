@@ -14,18 +14,25 @@ from .base import Norm, WeightSpec, VECTOR
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
-    def __init__(self, dim: int, eps: float, name: str = "weight", prefix: str = ""):
+    def __init__(self, dim: int, eps: float, name: str = "weight", weight_offset: float = 0.0, prefix: str = ""):
         super().__init__(prefix)
         self.dim = int(dim)
         self.eps = float(eps)
         self.name = name                  # the weight's tensor name relative to the prefix
+        # a weight stored around zero: the multiplier is weight_offset + w (1 + w in the designs that do this); the sum
+        # is taken once, in float32, when the tensor is loaded
+        self.weight_offset = float(weight_offset)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
+        if self.weight_offset != 0.0:
+            return {self.name: WeightSpec((self.dim,), VECTOR, init="normal", init_scale=0.1)}
         return {self.name: WeightSpec((self.dim,), VECTOR, init="one_plus_normal")}
 
     def load(self, tensors, ops, act_dtype) -> None:
         self.weight = tensors[self.name]
+        if self.weight_offset != 0.0:
+            self.weight = (self.weight.to(torch.float32) + self.weight_offset).contiguous()
 
     def deferred(self, x, ops, out_dtype):
         """The norm of ``x`` as an object that the kernel library's products can fold in, or None when the
