@@ -56,7 +56,7 @@ def softmax_rows(scores, visible):
 
 
 def biased_chunk_attention(h, wq, wk, wv, wo, temp, r1, r2, heads: int, kv_heads: int, dim: int, vdim: int,
-                           scale: float, chunk: int):
+                           scale: float, chunk: int, window: int = 0):
     """Grouped heads without rotation.  score(i, j) = q_i.k_j * scale * temp_h - r1_h * ln(1 + r2_h * (i - j)) for
     j <= i in the same block of ``chunk`` positions (blocks counted from position 0); chunk 0 = all j <= i."""
     T = h.shape[0]
@@ -68,10 +68,14 @@ def biased_chunk_attention(h, wq, wk, wv, wo, temp, r1, r2, heads: int, kv_heads
     visible = pos[None, :] <= pos[:, None]
     if chunk > 0:
         visible = visible & ((pos[:, None] // chunk) == (pos[None, :] // chunk))
+    if window > 0:
+        visible = visible & (pos[None, :] > pos[:, None] - window)
     outs = []
     for hd in range(heads):
         g = hd // (heads // kv_heads)
-        s = (q[:, hd] @ k[:, g].T) * scale * temp[hd] - r1[hd] * torch.log1p(r2[hd] * dist)
+        s = (q[:, hd] @ k[:, g].T) * scale * (temp[hd] if temp is not None else 1.0)
+        if r1 is not None:
+            s = s - r1[hd] * torch.log1p(r2[hd] * dist)
         outs.append(softmax_rows(s, visible) @ v[:, g])
     return torch.cat(outs, dim=-1) @ wo.T
 
@@ -91,24 +95,25 @@ def min_gru(h, wz, bz, wx, bx, wg, wo, state=None):
     return mixed @ wo.T, S
 
 
-def latent_of(h, wdkv, dkv_norm, eps: float, kv_rank: int, rot_base: float, rot_dim: int):
-    """What a latent attention layer keeps of every token: (c [T, kv_rank] normed, r [T, rot_dim] rotated)."""
+def latent_of(h, wdkv, dkv_norm, eps: float, kv_rank: int, rot_base: float, rot_dim: int, rot_dims: int = 0):
+    """What a latent attention layer keeps of every token: (c [T, kv_rank] normed, r [T, rot_dim] with its first
+    ``rot_dims`` (0: all) elements rotated)."""
     T = h.shape[0]
     d = h @ wdkv.T
     c = rms_norm(d[:, :kv_rank], dkv_norm, eps, unit_offset=False)
-    r = rotate_pairs(d[:, kv_rank:kv_rank + rot_dim], torch.arange(T), rot_base, rot_dim)
+    r = rotate_pairs(d[:, kv_rank:kv_rank + rot_dim], torch.arange(T), rot_base, rot_dims or rot_dim)
     return c, r
 
 
 def latent_attention(h, c, r, wdq, dq_norm, wuq, wuk, wuv, wo, eps: float, heads: int, dim: int, rot_dim: int,
-                     vdim: int, scale: float, rot_base: float):
+                     vdim: int, scale: float, rot_base: float, rot_dims: int = 0):
     """Queries through a normed latent; per head [dim plain | rot_dim rotated]; keys W_uk c beside the shared r;
     values W_uv c; causal softmax of (q_plain.k_plain + q_rot.r) * scale."""
     T = h.shape[0]
     cq = rms_norm(h @ wdq.T, dq_norm, eps, unit_offset=False)
     q = (cq @ wuq.T).reshape(T, heads, dim + rot_dim)
     q_plain = q[..., :dim]
-    q_rot = rotate_pairs(q[..., dim:].contiguous(), torch.arange(T), rot_base, rot_dim)
+    q_rot = rotate_pairs(q[..., dim:].contiguous(), torch.arange(T), rot_base, rot_dims or rot_dim)
     k_plain = (c @ wuk.T).reshape(T, heads, dim)
     v = (c @ wuv.T).reshape(T, heads, vdim)
     pos = torch.arange(T)
@@ -120,17 +125,22 @@ def latent_attention(h, c, r, wdq, dq_norm, wuq, wuk, wuv, wo, eps: float, heads
     return torch.cat(outs, dim=-1) @ wo.T
 
 
-def routed_experts(h, w_router, experts: List[Dict[str, torch.Tensor]], top: int):
+def routed_experts(h, w_router, experts: List[Dict[str, torch.Tensor]], top: int, weight_on: str = "input",
+                   renormalize: bool = False):
     """s = sigmoid(W_r h); the ``top`` experts of largest s; out = sum_e down_e(silu(gate_e(s_e h)) * up_e(s_e h)):
-    the score scales the expert's input, and the scores are used as they are."""
+    the score scales the expert's input, and the scores are used as they are.  (``weight_on`` "output": the score
+    scales the expert's output instead; ``renormalize``: the chosen scores are divided by their sum.)"""
     s = torch.sigmoid(h @ w_router.T)
     out = torch.zeros(h.shape[0], experts[0]["down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         order = sorted(range(len(experts)), key=lambda e: (-float(s[t, e]), e))[:top]
+        total = sum(s[t, e] for e in order) if renormalize else 1.0
         for e in order:
-            xin = s[t, e] * h[t]
+            wt = s[t, e] / total
+            xin = wt * h[t] if weight_on == "input" else h[t]
             w = experts[e]
-            out[t] += w["down"] @ (silu(w["gate"] @ xin) * (w["up"] @ xin))
+            y = w["down"] @ (silu(w["gate"] @ xin) * (w["up"] @ xin))
+            out[t] += y if weight_on == "input" else wt * y
     return out
 
 
@@ -140,7 +150,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
     Wt = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = float(config["norm"]["eps"])
     T = len(tokens)
-    x = Wt["embed"][torch.tensor(list(tokens), dtype=torch.long)] * float(config["embedding"]["scale"])
+    x = Wt["embed"][torch.tensor(list(tokens), dtype=torch.long)] * float((config.get("embedding") or {}).get("scale", 1.0))
     kept = {}
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}", layer["mixer"]
@@ -154,17 +164,18 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
                 int(L["mask"]["size"]) if L.get("mask") else 0)
             right, _ = min_gru(h, Wt[f"{p}.mix.right.z"], Wt[f"{p}.mix.right.z.b"], Wt[f"{p}.mix.right.x"],
                                Wt[f"{p}.mix.right.x.b"], Wt[f"{p}.mix.right.g"], Wt[f"{p}.mix.right.o"])
-            y = float(m["left_scale"]) * left + float(m["right_scale"]) * right
+            y = float(m.get("left_scale", 1.0)) * left + float(m.get("right_scale", 1.0)) * right
         elif layer["type"] == "latent_attention":
             base, rdim = float(m["rot"]["base"]), int(m["rot_dim"])
+            rdims = int(m["rot"].get("dims", rdim))
             if m.get("kv_from") is None:
-                kept[i] = latent_of(h, Wt[f"{p}.mix.dkv"], Wt[f"{p}.mix.dkv.norm"], eps, int(m["kv_rank"]), base, rdim)
+                kept[i] = latent_of(h, Wt[f"{p}.mix.dkv"], Wt[f"{p}.mix.dkv.norm"], eps, int(m["kv_rank"]), base, rdim, rdims)
                 c, r = kept[i]
             else:
                 c, r = kept[int(m["kv_from"])]
             y = latent_attention(h, c, r, Wt[f"{p}.mix.dq"], Wt[f"{p}.mix.dq.norm"], Wt[f"{p}.mix.uq"],
                                  Wt[f"{p}.mix.uk"], Wt[f"{p}.mix.uv"], Wt[f"{p}.mix.o"], eps, int(m["heads"]),
-                                 int(m["dim"]), rdim, int(m["vdim"]), float(m["scale"]), base)
+                                 int(m["dim"]), rdim, int(m["vdim"]), float(m["scale"]), base, rdims)
         else:
             raise ValueError(layer["type"])
         x = x + y
