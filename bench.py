@@ -551,19 +551,112 @@ def run_tipezen(steps: int, warmup: int) -> int:
             torch.cuda.empty_cache()
     return 0
 
+# The Dominex design beside Tipezen (the closest of the other models: layers listed one by one, a windowed attention
+# beside a recurrence with state slots) at the same width: (width, latent heads, dim, rot_dim, vdim, q_rank, kv_rank,
+# left heads, left kv heads, left dim, block, recurrence width, experts, chosen, expert ff).  Four layers of two mixers
+# side by side alternate with four latent attention layers (one of them reading its neighbour's vectors); the latent
+# layers carry the experts, whose chosen share equals the twin's dense feed-forward.
+DOMINEX_SIZES = {"2k": (2048, 16, 128, 64, 128, 768, 512, 16, 4, 128, 1024, 2048, 16, 2, 3072),
+                 "4k": (4096, 32, 128, 64, 128, 1536, 512, 32, 8, 128, 2048, 4096, 16, 2, 6144)}
+
+
+def dominex_engine(size: str, max_live: int, cache_tokens: int, graphs: bool, step_tokens: int):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config import DominexConfig, DominexLayer, DominexExperts
+    from tffinfer_b200.weights import random_tensors_on_device
+    W, H, D, R, VD, QR, KR, LH, LG, LD, CH, RW, E, TOP, F = DOMINEX_SIZES[size]
+    moe = DominexExperts(ff=F, experts=E, top=TOP)
+    lat = lambda src: DominexLayer(type="latent_attention", heads=H, dim=D, rot_dim=R, vdim=VD, q_rank=QR, kv_rank=KR,
+                                   scale=(D + R) ** -0.5, rot_base=5e5, rot_dims=R, kv_from=src, mlp=moe)
+    par = DominexLayer(type="parallel", left_heads=LH, left_kv_heads=LG, left_dim=LD, left_vdim=LD, left_scale_qk=LD ** -0.5,
+                       left_chunk=CH, right_width=RW, left_scale=0.8, right_scale=0.9)
+    layers = tuple(par if i % 2 == 0 else lat(1 if i == 5 else None) for i in range(TIPEZEN_LAYERS))
+    cfg = DominexConfig("Dominex", vocab_size=TIPEZEN_VOCAB, hidden_size=W, embed_scale=W ** 0.5, norm_eps=1e-6,
+                        logit_softcap=30.0, layers=layers)
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens, max_live_requests=max_live,
+                            max_tokens_per_step=step_tokens, max_model_len=8192, use_cuda_graphs=graphs)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def run_dominex(steps: int, warmup: int, sizes=None) -> int:
+    """Prefill and decode throughput of the Dominex design beside Tipezen at the same layer sizes, one JSON line a
+    point, and for each model the device time of a step by kind of kernel call; for Dominex also what its own
+    kernels reach: the attention tiles and the grouped products in TFLOP/s, the recurrence and the small kernels
+    around the experts as a fraction of the measured copy rate."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 32)
+    P = PROMPT_LEN
+    for size in (sizes or DOMINEX_SIZES):
+        W, H, D, R, VD, QR, KR, LH, LG, LD, CH, RW, E, TOP, F = DOMINEX_SIZES[size]
+        for model, make in (("dominex", dominex_engine), ("tipezen", tipezen_engine)):
+            need = 64 * (P + warmup + steps + 64 + 72)
+            engine, cfg = make(size, 64, need, True, P)
+            pms = prefill_run(engine, iters=3, warmup=2, seed=1, prompt_len=P)
+            print(json.dumps({"point": "prefill", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "tokens": P,
+                              "ms": round(pms, 3), "tok_s": round(P / (pms / 1e3), 1)}), flush=True)
+            for b in (8, 64):
+                run = decode_run(engine, b, steps, warmup, seed=b, prompt_len=P)
+                print(json.dumps({"point": "decode", "model": model, "size": size, "layers": TIPEZEN_LAYERS, "batch": b,
+                                  "context": round(run["mean_context"]), "tok_s": round(run["tok_s"], 1),
+                                  "ms_per_step": round(run["ms_per_step"], 4), "launches_per_step": run["launches"] // steps}),
+                      flush=True)
+            del engine
+            torch.cuda.empty_cache()
+            engine, cfg = make(size, 8, 8 * (P + 64), False, P)
+            kinds = traced_kinds(engine, P, 8)
+            line = {"point": "kernels", "model": model, "size": size, "prefill_tokens": P, "decode_batch": 8,
+                    "prefill_ms_by_kind": kinds.get("prefill"), "decode_ms_by_kind": kinds.get("decode"), "peaks": peaks["source"]}
+            if model == "dominex":
+                nl = TIPEZEN_LAYERS // 2
+                # prompt step: causal scores and weighted sums of the latent layers (keys of KR + R, values of KR
+                # elements, H heads) and of the chunked layers (LD and LD, LH heads, blocks of CH positions)
+                pairs = lambda T, span: T * (min(T, span) + 1) / 2.0 if span >= T else T * (span + 1) / 2.0
+                attn_flops = nl * H * pairs(P, P) * 2.0 * (2 * KR + R) + nl * LH * pairs(P, CH) * 2.0 * (2 * LD)
+                grouped_flops = nl * (P * TOP * 3 * 2.0 * W * F + P * H * 2.0 * KR * (D + VD))
+                gru_bytes = lambda T: nl * T * RW * (3 * 4 + 2)
+                fr = {}
+                k = kinds.get("prefill") or {}
+                if "attention_tile" in k:
+                    fr["prefill_attention_tile_tflops"] = round(attn_flops / (k["attention_tile"][1] / 1e3) / 1e12, 2)
+                if "gemm_grouped" in k:
+                    fr["prefill_gemm_grouped_tflops"] = round(grouped_flops / (k["gemm_grouped"][1] / 1e3) / 1e12, 2)
+                if "min_gru" in k:
+                    fr["prefill_min_gru_hbm_frac"] = round(gru_bytes(P) / (k["min_gru"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                kd = kinds.get("decode") or {}
+                if "attention_tile" in kd:
+                    # decode: every request's cached vectors (latent) and the keys and values of its block are read once
+                    cache_b = 8 * (3 * P * (KR + R) * 2 + nl * min(P, CH) * 2 * LG * LD * 2)
+                    fr["decode_attention_tile_hbm_frac"] = round(cache_b / (kd["attention_tile"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                if "gemm_grouped" in kd:
+                    # decode: the chosen experts' weights (at most 8 * TOP different ones of E) and the heads' up-projections
+                    w_b = nl * (min(E, 8 * TOP) * 3 * W * F * 2 + H * KR * (D + VD) * 2)
+                    fr["decode_gemm_grouped_hbm_frac"] = round(w_b / (kd["gemm_grouped"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                line["fractions"] = fr
+            print(json.dumps(line), flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    return 0
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes", "tipezen", "dominex"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
                          "context lengths; attn_decode: the decode attention alone; shapes: the layer sizes of the other "
-                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; else a whole workload through "
+                         "models of the family; tipezen: the Tipezen design beside Qwen3 at equal layer sizes; dominex: the Dominex design beside Tipezen at equal layer sizes; else a whole workload through "
                          "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--size", default="", help="with --workload dominex: one of its layer sizes (2k, 4k) instead of all")
     ap.add_argument("--layers", type=int, default=SHAPE["num_layers"],
                     help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no batch 1 / 64, no prefill)")
@@ -588,6 +681,8 @@ def main() -> int:
         return run_shapes(args.steps, warmup)
     if args.workload == "tipezen":
         return run_tipezen(args.steps, warmup)
+    if args.workload == "dominex":
+        return run_dominex(args.steps, warmup, [args.size] if args.size else None)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 

@@ -253,7 +253,7 @@ def test_min_gru_steps_and_slots(ops, width):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,top,ff,W,T", [(5, 1, 24, 40, 70), (7, 3, 64, 128, 130), (3, 3, 10, 52, 9), (1, 1, 16, 64, 3),
-                                           (64, 6, 32, 64, 200)])
+                                           (64, 6, 32, 64, 200), (6, 2, 200, 136, 700)])
 def test_routed_experts(ops, dtype, E, top, ff, W, T):
     """Route, sort by expert, the two grouped products and the sum, against the plain loop over tokens; the weight on
     the experts' input (as they are) and on their output (renormalised)."""
@@ -263,13 +263,14 @@ def test_routed_experts(ops, dtype, E, top, ff, W, T):
     wr = (torch.randn(E, W, generator=g) * 0.5).to(dt)
     ex = [{"gate": (torch.randn(ff, W, generator=g) * W ** -0.5).to(dt), "up": (torch.randn(ff, W, generator=g) * W ** -0.5).to(dt),
            "down": (torch.randn(W, ff, generator=g) * ff ** -0.5).to(dt)} for _ in range(E)]
-    stack = lambda k: torch.stack([e[k] for e in ex]).to(dev).contiguous()
+    gate_up, layout = ops.stack_gate_up([e["gate"].to(dev) for e in ex], [e["up"].to(dev) for e in ex])
+    down = torch.stack([e["down"] for e in ex]).to(dev).contiguous()
     res = torch.randn(T, W, generator=g)
     for weight_on, renorm in (("input", False), ("output", True)):
         want = res.double() + P.routed_experts(h.double(), wr.double(), [{k: v.double() for k, v in e.items()} for e in ex],
                                                top, weight_on, renorm)
         out = res.clone().to(dev)
-        ops.routed_mlp(h.to(dev), wr.to(dev), stack("gate"), stack("up"), stack("down"), out, top, renorm, weight_on, "silu")
+        ops.routed_mlp(h.to(dev), wr.to(dev), gate_up, layout, down, out, top, renorm, weight_on, "silu")
         torch.cuda.synchronize()
         err = float((out.double().cpu() - want).abs().max() / want.abs().max())
         assert err < (2e-5 if dtype == "float32" else 3e-2), f"{weight_on}: off by {err:.3g}"
@@ -356,6 +357,25 @@ def test_grouped_product_of_column_blocks(ops):
         want = a[:, i * K:(i + 1) * K].double() @ b[i].double().T
         assert float((c[:, i * N:(i + 1) * N].double() - want).abs().max()) < 1e-4
     assert torch.isnan(c[:, G * N:]).all()
+
+
+@pytest.mark.parametrize("M,N,K,G", [(300, 72, 40, 3), (5, 256, 512, 2), (129, 8, 8, 1)])
+def test_grouped_product_on_tensor_cores(ops, M, N, K, G):
+    """bfloat16 operands of aligned sizes take the tensor-core kernel: against torch on the same bfloat16 values, for
+    tiles that are full, ragged in rows, in columns and in K."""
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(M, G * K + 8, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(G, N, K, generator=g).to(torch.bfloat16).cuda()
+    assert ops.grouped_on_tensor_cores(a, b, K, a.shape[1], K, K, N * K, "", N)
+    for dt in (torch.float32, torch.bfloat16):
+        c = torch.full((M, G * N + 2), float("nan"), dtype=dt).cuda()
+        ops.gemm_grouped(a, b, c, G, M, N, K, a.shape[1], K, K, N * K, c.shape[1], N)
+        torch.cuda.synchronize()
+        for i in range(G):
+            want = a[:, i * K:(i + 1) * K].double() @ b[i].double().T
+            err = float((c[:, i * N:(i + 1) * N].double() - want).abs().max() / want.abs().max())
+            assert err < (1e-5 if dt == torch.float32 else 1e-2), err
+        assert torch.isnan(c[:, G * N:]).all()
 
 
 # ------------------------------------------------------------------------------ generation through the engine

@@ -29,7 +29,7 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
                     TCc* __restrict__ C, long long ldc, long long c_gs,
                     const int* __restrict__ tile_group, const int* __restrict__ tile_row0,
                     const int* __restrict__ tile_row_end, const int* __restrict__ num_tiles,
-                    const int* __restrict__ row_map, int M, int N, int K, int act) {
+                    const int* __restrict__ row_map, int M, int N, int K, int act, int b_interleaved) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     __shared__ float Bs2[GATED ? BK : 1][BN + 4];
@@ -63,8 +63,11 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
             if (gk < K) {
                 if (m0 + r < m_end) a = to_f32<TA>(Ag[(size_t)(m0 + r) * lda + gk]);
                 if (n0 + r < N) {
-                    w = to_f32<TB>(Bg[(size_t)(n0 + r) * ldb + gk]);
-                    if constexpr (GATED) w2 = to_f32<TB>(B2g[(size_t)(n0 + r) * ldb + gk]);
+                    // interleaved: output column n has its gate row at (n / 8) * 16 + n % 8 and its up row 8 further (B2 = B + 8 rows)
+                    const int n = n0 + r;
+                    const size_t brow = b_interleaved ? (size_t)(n >> 3) * 16 + (n & 7) : (size_t)n;
+                    w = to_f32<TB>(Bg[brow * ldb + gk]);
+                    if constexpr (GATED) w2 = to_f32<TB>(B2g[brow * ldb + gk]);
                 }
             }
             As[kk][r] = a;
@@ -109,6 +112,7 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
 }  // namespace
 
 // dt codes: 0 = float32, 1 = bfloat16.  B2 null = plain product; else gated with ``act`` (0 silu, 1 tanh-gelu).
+// b_interleaved (gated only): the gate and up rows of a group lie interleaved in eights in ONE matrix (B2 = B + 8 rows).
 // Uniform: tile_group null, ``groups`` groups of M rows.  Ragged: the four tile arrays on the device, ``max_tiles`` the
 // grid's size, M unused, c_gs and a_gs usually 0.
 TFF_API int tff_gemm_grouped(
@@ -116,7 +120,7 @@ TFF_API int tff_gemm_grouped(
     const void* B, const void* B2, int b_dt, long long ldb, long long b_gs,
     void* C, int c_dt, long long ldc, long long c_gs,
     const int* tile_group, const int* tile_row0, const int* tile_row_end, const int* num_tiles, int max_tiles,
-    const int* row_map, int groups, int M, int N, int K, int act, cudaStream_t stream) {
+    const int* row_map, int groups, int M, int N, int K, int act, int b_interleaved, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || !A || !B || !C) return TFF_ERR_BAD_ARGUMENT;
     dim3 grid;
     if (tile_group) {
@@ -134,10 +138,10 @@ TFF_API int tff_gemm_grouped(
         if (B2)                                                                                                      \
             return tff_launch_pdl(gemm_grouped_kernel<TA, TB, TCc, true>, grid, dim3(256), 0, stream, (const TA*)A, lda, a_gs, \
                                   (const TB*)B, (const TB*)B2, ldb, b_gs, (TCc*)C, ldc, c_gs, tile_group, tile_row0,   \
-                                  tile_row_end, num_tiles, row_map, M, N, K, act);                                   \
+                                  tile_row_end, num_tiles, row_map, M, N, K, act, b_interleaved);                                   \
         return tff_launch_pdl(gemm_grouped_kernel<TA, TB, TCc, false>, grid, dim3(256), 0, stream, (const TA*)A, lda, a_gs,   \
                               (const TB*)B, (const TB*)nullptr, ldb, b_gs, (TCc*)C, ldc, c_gs, tile_group, tile_row0, \
-                              tile_row_end, num_tiles, row_map, M, N, K, act);                                       \
+                              tile_row_end, num_tiles, row_map, M, N, K, act, b_interleaved);                                       \
     } while (0)
     if (a_dt == 0 && b_dt == 0 && c_dt == 0) TFF_GG(float, float, float);
     if (a_dt == 0 && b_dt == 1 && c_dt == 0) TFF_GG(float, bf16, float);

@@ -9,7 +9,8 @@
 //   (a cache of ONE plane: a token's slot holds [c | r]; kv_rank = 0 or no cache: a layer that reads another layer's)
 // rmsnorm(x) = x * rsqrt(mean(x^2) + eps), then times the weight; all float32, only the stores round.
 //
-// latent_q_rot, one warp per (token, head): the rotated part of a query head, q[t, h*(dim+rot_dim) + dim ..], turned
+// latent_q_rot, one warp per (token, head): the rotated part of a query head, q[t, h*(dim+rot_dim) + dim ..] (the
+// up-projection's output in the activation type; the rotation itself is float32), turned
 // the same way, into columns kv_rank .. of the head's row of the absorbed query [T, heads*(kv_rank+rot_dim)].
 #include "common.cuh"
 
@@ -73,7 +74,7 @@ latent_finish_kernel(float* __restrict__ proj, int ld, int clear_input, int q_ra
 
 template <typename TQ>
 __global__ void __launch_bounds__(128)
-latent_q_rot_kernel(const float* __restrict__ q, int dim, int rot_dim, int rot_dims, const float* __restrict__ freq,
+latent_q_rot_kernel(const TQ* __restrict__ q, int dim, int rot_dim, int rot_dims, const float* __restrict__ freq,
                     const int* __restrict__ positions, TQ* __restrict__ q_lat, int kv_rank, int heads, int num_tokens) {
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,17 +83,17 @@ latent_q_rot_kernel(const float* __restrict__ q, int dim, int rot_dim, int rot_d
     const int t = (int)(item / heads), h = (int)(item % heads);
     const int pos = positions[t];
     pdl_wait();
-    const float* src = q + ((size_t)t * heads + h) * (dim + rot_dim) + dim;
+    const TQ* src = q + ((size_t)t * heads + h) * (dim + rot_dim) + dim;
     TQ* dst = q_lat + ((size_t)t * heads + h) * (kv_rank + rot_dim) + kv_rank;
     const int half = rot_dims >> 1;
     for (int i = lane; i < half; i += 32) {
-        const float u = src[2 * i], v = src[2 * i + 1];
+        const float u = to_f32<TQ>(src[2 * i]), v = to_f32<TQ>(src[2 * i + 1]);
         float s, c;
         sincosf((float)pos * freq[i], &s, &c);
         dst[2 * i] = from_f32<TQ>(u * c - v * s);
         dst[2 * i + 1] = from_f32<TQ>(v * c + u * s);
     }
-    for (int i = 2 * half + lane; i < rot_dim; i += 32) dst[i] = from_f32<TQ>(src[i]);
+    for (int i = 2 * half + lane; i < rot_dim; i += 32) dst[i] = src[i];
 }
 
 }  // namespace
@@ -119,15 +120,15 @@ TFF_API int tff_latent_finish(float* proj, int ld, int clear_input, int q_rank, 
                           table_width, (float*)cache, page_stride, page_size, slot_elems, (float*)cq);
 }
 
-TFF_API int tff_latent_q_rot(const float* q, int dim, int rot_dim, int rot_dims, const float* freq, const int* positions,
+TFF_API int tff_latent_q_rot(const void* q, int dim, int rot_dim, int rot_dims, const float* freq, const int* positions,
                              void* q_lat, int is_bf16, int kv_rank, int heads, int num_tokens, cudaStream_t stream) {
     if (num_tokens <= 0 || rot_dim <= 0) return TFF_OK;
     if (!q || !q_lat || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims > 0 && !freq)) return TFF_ERR_BAD_ARGUMENT;
     const long long items = (long long)num_tokens * heads;
     dim3 grid((unsigned)((items + 3) / 4));
     if (is_bf16)
-        return tff_launch_pdl(latent_q_rot_kernel<bf16>, grid, dim3(128), 0, stream, q, dim, rot_dim, rot_dims, freq, positions,
+        return tff_launch_pdl(latent_q_rot_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)q, dim, rot_dim, rot_dims, freq, positions,
                               (bf16*)q_lat, kv_rank, heads, num_tokens);
-    return tff_launch_pdl(latent_q_rot_kernel<float>, grid, dim3(128), 0, stream, q, dim, rot_dim, rot_dims, freq, positions,
+    return tff_launch_pdl(latent_q_rot_kernel<float>, grid, dim3(128), 0, stream, (const float*)q, dim, rot_dim, rot_dims, freq, positions,
                           (float*)q_lat, kv_rank, heads, num_tokens);
 }

@@ -686,50 +686,108 @@ class CudaKernels:
 
     # ------------------------------------------------------- many small products in one launch
     def gemm_grouped(self, a, b, c, groups: int, M: int, N: int, K: int, lda: int, a_gs: int, ldb: int, b_gs: int,
-                     ldc: int, c_gs: int, b2=None, activation: str = "silu", tiles=None, row_map=None) -> None:
-        """c_g = a_g @ b_g^T for ``groups`` groups whose operands lie a_gs, b_gs, c_gs elements apart (rows lda, ldb,
-        ldc elements apart), in float32 FMAs with a fixed order of additions.  With ``b2``: act(a b^T) * (a b2^T).
-        ``tiles`` = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles) is the ragged form (rows of ``a`` sorted
-        by group, the table on the device); ``row_map`` sends product row r to row row_map[r] of ``c``."""
-        self._need_cuda(a, b, c, b2, row_map)
-        assert b2 is None or b2.dtype == b.dtype
+                     ldc: int, c_gs: int, gated: str = "", activation: str = "silu", tiles=None, row_map=None) -> None:
+        """c_g = a_g @ b_g^T ([M, K] x [N, K]^T) for ``groups`` groups whose operands lie a_gs, b_gs, c_gs elements apart
+        (rows lda, ldb, ldc elements apart), float32 accumulation with a fixed order of additions.  ``gated``: b_g holds
+        2N rows, gate and up, "blocked" ([N gate | N up]) or "interleaved" (in eights: stack_gate_up), and
+        c_g = act(a gate^T) * (a up^T).  ``tiles`` = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, tile rows)
+        is the ragged form (rows of ``a`` sorted by group, the table on the device); ``row_map`` sends product row r to
+        row row_map[r] of ``c``.  bfloat16 operands of aligned sizes run on the tensor cores (csrc/gemm_grouped_mma.cu),
+        everything else as float32 FMAs (csrc/gemm_grouped.cu)."""
+        self._need_cuda(a, b, c, row_map)
+        assert gated in ("", "blocked", "interleaved")
         tg = tr0 = tre = nt = None
-        max_tiles = 0
+        max_tiles, tile_rows = 0, 0
         if tiles is not None:
-            tg, tr0, tre, nt, max_tiles = tiles
+            tg, tr0, tre, nt, max_tiles, tile_rows = tiles
+        act = _c_int(self.ACTIVATION_CODES[activation])
+        ll = ctypes.c_longlong
+        if self.grouped_on_tensor_cores(a, b, K, lda, a_gs, ldb, b_gs, gated, N) and tile_rows in (0, self.grouped_tile_rows(True)):
+            status = self.lib.tff_gemm_grouped_mma(
+                _ptr(a), ll(lda), ll(a_gs), _ptr(b), ll(ldb), ll(b_gs), _ptr(c), _c_int(_dt(c)), ll(ldc), ll(c_gs),
+                _ptr(tg), _ptr(tr0), _ptr(tre), _ptr(nt), _c_int(max_tiles), _ptr(row_map), _c_int(groups), _c_int(M),
+                _c_int(2 * N if gated else N), _c_int(K), _c_int(1 if gated else 0), act, self._stream())
+            self._check(status, "gemm_grouped_mma")
+            self.launches += 1
+            return
+        assert tile_rows in (0, self.grouped_tile_rows(False)), "the tile table was planned for the other kernel"
+        b2 = _vp(0)
+        if gated:
+            b2 = _vp(b.data_ptr() + (8 if gated == "interleaved" else N) * ldb * b.element_size())
         self._check(self.lib.tff_gemm_grouped(
-            _ptr(a), _c_int(_dt(a)), ctypes.c_longlong(lda), ctypes.c_longlong(a_gs),
-            _ptr(b), _ptr(b2), _c_int(_dt(b)), ctypes.c_longlong(ldb), ctypes.c_longlong(b_gs),
-            _ptr(c), _c_int(_dt(c)), ctypes.c_longlong(ldc), ctypes.c_longlong(c_gs),
-            _ptr(tg), _ptr(tr0), _ptr(tre), _ptr(nt), _c_int(max_tiles), _ptr(row_map),
-            _c_int(groups), _c_int(M), _c_int(N), _c_int(K), _c_int(self.ACTIVATION_CODES[activation]),
-            self._stream()), "gemm_grouped")
+            _ptr(a), _c_int(_dt(a)), ll(lda), ll(a_gs), _ptr(b), b2, _c_int(_dt(b)), ll(ldb), ll(b_gs),
+            _ptr(c), _c_int(_dt(c)), ll(ldc), ll(c_gs), _ptr(tg), _ptr(tr0), _ptr(tre), _ptr(nt), _c_int(max_tiles),
+            _ptr(row_map), _c_int(groups), _c_int(M), _c_int(N), _c_int(K), act,
+            _c_int(1 if gated == "interleaved" else 0), self._stream()), "gemm_grouped")
         self.launches += 1
 
+    GROUPED_MMA = os.environ.get("TFFINFER_GROUPED_MMA", "1") != "0"
+
+    def grouped_on_tensor_cores(self, a, b, K, lda, a_gs, ldb, b_gs, gated: str, N: int) -> bool:
+        """Whether a grouped product of these operands runs on the tensor-core kernel."""
+        return (self.GROUPED_MMA and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+                and all(v % 8 == 0 for v in (K, lda, a_gs, ldb, b_gs)) and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+                and (not gated or (gated == "interleaved" and N % 8 == 0)))
+
+    def grouped_tile_rows(self, tensor_cores: bool) -> int:
+        return int(self.lib.tff_gemm_grouped_mma_tile_rows() if tensor_cores else self.lib.tff_gemm_grouped_tile_rows())
+
+    @staticmethod
+    def stack_gate_up(gates, ups):
+        """One tensor [E, 2*ff, W] from the experts' gate and up matrices, and the name of its layout: "interleaved"
+        (rows in eights: eight gate rows, the eight up rows of the same outputs, ...; what the tensor-core kernel's
+        epilogue wants) when ff is a multiple of 8, else "blocked" (all gate rows, then all up rows)."""
+        g, u = torch.stack(list(gates), dim=0), torch.stack(list(ups), dim=0)
+        E, ff, W = g.shape
+        if ff % 8 == 0:
+            w = torch.stack([g.view(E, ff // 8, 8, W), u.view(E, ff // 8, 8, W)], dim=2).reshape(E, 2 * ff, W)
+            return w.contiguous(), "interleaved"
+        return torch.cat([g, u], dim=1).contiguous(), "blocked"
+
     # ------------------------------------------------------- routed feed-forward (mixture of experts)
-    def routed_mlp(self, h, w_router, w_gate, w_up, w_down, residual, top: int, renormalize: bool = False,
+    def routed_mlp(self, h, w_router, w_gate_up, layout: str, w_down, residual, top: int, renormalize: bool = False,
                    weight_on: str = "output", activation: str = "silu", out=None) -> None:
         """residual += sum over a token's ``top`` experts of down_e(act(gate_e(x)) * up_e(x)), the experts chosen by
         the largest sigmoid(W_r h) (computed in float32), weights the scores themselves or renormalised to sum 1;
         ``weight_on`` "input": x = w h and the outputs are summed as they are; "output": x = h and the outputs are
-        summed with the weights.  w_gate, w_up [E, ff, W], w_down [E, W, ff].  With ``residual`` None the sum goes to
-        ``out``.  Six launches, no host synchronisation: route, plan, gather, two grouped products over the tokens
-        sorted by expert, combine (a token's experts are added in the order of their rank)."""
+        summed with the weights.  (w_gate_up, layout) = stack_gate_up(...) [E, 2*ff, W], w_down [E, W, ff].  With
+        ``residual`` None the sum goes to ``out``.  Six launches, no host synchronisation: route, plan, gather, two
+        grouped products over the tokens sorted by expert, combine (a token's experts are added in the order of their
+        rank)."""
         if isinstance(h, DeferredNorm):
             h = h.materialize()
-        self._need_cuda(h, w_router, w_gate, w_up, w_down, residual, out)
+        self._need_cuda(h, w_router, w_gate_up, w_down, residual, out)
         T, W = h.shape
-        E, ff = w_gate.shape[0], w_gate.shape[1]
-        assert tuple(w_router.shape) == (E, W) and tuple(w_up.shape) == (E, ff, W) and tuple(w_down.shape) == (E, W, ff)
+        E, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+        assert tuple(w_router.shape) == (E, W) and tuple(w_gate_up.shape) == (E, 2 * ff, W) and tuple(w_down.shape) == (E, W, ff)
         assert weight_on in ("input", "output") and 0 < top <= E
         target = residual if residual is not None else out
         assert target.dtype == torch.float32 and tuple(target.shape) == (T, W)
+        P = T * top
+        # both products run on the same kernel (one tile table): the tensor-core one if both can
+        tc = (self.grouped_on_tensor_cores(h, w_gate_up, W, W, 0, W, 2 * ff * W, layout, ff)
+              and self.grouped_on_tensor_cores(h, w_down, ff, ff, 0, ff, W * ff, "", W))
+        pair_weight, row_map, tiles, x = self.moe_dispatch(h, w_router, top, renormalize, weight_on == "input",
+                                                           self.grouped_tile_rows(tc))
+        act = torch.empty((P, ff), dtype=h.dtype, device=h.device)
+        self.gemm_grouped(x, w_gate_up, act, E, 0, ff, W, W, 0, W, 2 * ff * W, ff, 0, gated=layout, activation=activation,
+                          tiles=tiles)
+        y = torch.empty((P, W), dtype=torch.float32, device=h.device)
+        self.gemm_grouped(act, w_down, y, E, 0, W, ff, ff, 0, ff, W * ff, W, 0, tiles=tiles, row_map=row_map)
+        self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target)
+
+    def moe_dispatch(self, h, w_router, top: int, renormalize: bool, scale_rows: bool, tile_rows: int = 0):
+        """Router, choice and sorting of a routed feed-forward (csrc/moe.cu: route, plan, gather).  Returns
+        (pair_weight float32 [T*top], row_map int32 [T*top]: sorted place -> pair, the tile table of the grouped
+        products, x [T*top, W]: the tokens' rows sorted by expert, times their weight when ``scale_rows``)."""
+        T, W = h.shape
+        E = w_router.shape[0]
         dev, P = h.device, T * top
         counts = self._moe_counts.get((E, str(dev)))
         if counts is None:
             counts = torch.zeros(E, dtype=torch.int32, device=dev)       # set back to zero by the plan kernel
             self._moe_counts[(E, str(dev))] = counts
-        bm = int(self.lib.tff_gemm_grouped_tile_rows())
+        bm = tile_rows or self.grouped_tile_rows(False)      # rows of a tile of the grouped product that follows
         max_tiles = -(-P // bm) + E
         ints = torch.empty(2 * P + E + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
         pair_expert, row_map, cursor = ints[:P], ints[P:2 * P], ints[2 * P:2 * P + E]
@@ -744,16 +802,16 @@ class CudaKernels:
                                           _ptr(tile_row_end), _ptr(num_tiles), self._stream()), "moe_plan")
         x = torch.empty((P, W), dtype=h.dtype, device=dev)
         self._check(self.lib.tff_moe_gather(_ptr(h), _c_int(_dt(h)), _c_int(P), _c_int(W), _c_int(top), _ptr(pair_expert),
-                                            _ptr(pair_weight), _c_int(1 if weight_on == "input" else 0), _ptr(cursor),
+                                            _ptr(pair_weight), _c_int(1 if scale_rows else 0), _ptr(cursor),
                                             _ptr(row_map), _ptr(x), self._stream()), "moe_gather")
         self.launches += 3
-        tiles = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles)
-        act = torch.empty((P, ff), dtype=h.dtype, device=dev)
-        self.gemm_grouped(x, w_gate, act, E, 0, ff, W, W, 0, W, ff * W, ff, 0, b2=w_up, activation=activation, tiles=tiles)
-        y = torch.empty((P, W), dtype=torch.float32, device=dev)
-        self.gemm_grouped(act, w_down, y, E, 0, W, ff, ff, 0, ff, W * ff, W, 0, tiles=tiles, row_map=row_map)
+        return pair_weight, row_map, (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, bm), x
+
+    def moe_combine(self, y, pair_weight, top: int, residual, out) -> None:
+        """out[t] = residual[t] + sum_k w[t, k] * y[t*top + k] in the order of k (pair_weight None: plain sum)."""
+        T, W = out.shape
         self._check(self.lib.tff_moe_combine(_ptr(y), _c_int(T), _c_int(W), _c_int(top), _ptr(pair_weight),
-                                             _c_int(1 if weight_on == "output" else 0), _ptr(residual), _ptr(target),
+                                             _c_int(1 if pair_weight is not None else 0), _ptr(residual), _ptr(out),
                                              self._stream()), "moe_combine")
         self.launches += 1
 
@@ -801,31 +859,44 @@ class CudaKernels:
         proj = self.projection_buffer(T, w_down.shape[0], dev, dt)
         self.gemm(h, w_down, proj)
         cq = torch.empty((T, q_rank), dtype=dt, device=dev)
-        c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
-        clear = 1 if proj.data_ptr() in self._acc_zero else 0
-        self._need_cuda(q_norm_w, kv_norm_w, f, block_table)
-        self._check(self.lib.tff_latent_finish(
-            _ptr(proj), _c_int(proj.shape[1]), _c_int(clear), _c_int(q_rank), _c_int(kv_rank if write_cache else 0),
-            _c_int(rot_dim), _c_int(rot_dims), _ptr(q_norm_w), _ptr(kv_norm_w), _c_float(eps), _ptr(f),
-            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
-            c_ptr if write_cache else _vp(0), ctypes.c_longlong(page_stride), _c_int(page_size), _c_int(slot), _ptr(cq),
-            _c_int(_dt(cq)), _c_int(T), self._stream()), "latent_finish")
-        if clear:
-            self._acc_zero[proj.data_ptr()] = True
-        self.launches += 1
-        q = torch.empty((T, heads * (dim + rot_dim)), dtype=torch.float32, device=dev)
+        self.latent_finish(proj, cq, q_norm_w, kv_norm_w, eps, f, rot_dim, rot_dims, batch, block_table, kv_cache, kv_layer,
+                           page_size, q_rank, kv_rank if write_cache else 0)
+        q = torch.empty((T, heads * (dim + rot_dim)), dtype=dt, device=dev)
         self.gemm(cq, w_uq, q)
         q_lat = torch.empty((T, heads * slot), dtype=dt, device=dev)
         self.gemm_grouped(q, w_uk_t, q_lat, heads, T, kv_rank, dim, heads * (dim + rot_dim), dim + rot_dim,
                           dim, kv_rank * dim, heads * slot, slot)
-        self._check(self.lib.tff_latent_q_rot(_ptr(q), _c_int(dim), _c_int(rot_dim), _c_int(rot_dims), _ptr(f),
-                                              _ptr(batch.positions), _ptr(q_lat), _c_int(_dt(q_lat)), _c_int(kv_rank),
-                                              _c_int(heads), _c_int(T), self._stream()), "latent_q_rot")
-        self.launches += 1
+        self.latent_q_rot(q, q_lat, f, batch, heads, dim, rot_dim, rot_dims, kv_rank)
         o_lat = torch.empty((T, heads * kv_rank), dtype=dt, device=dev)
         self.attention_tile(q_lat, batch, block_table, kv_cache, kv_layer, page_size, o_lat, heads, 1, slot, kv_rank, scale)
         self.gemm_grouped(o_lat, w_uv, out, heads, T, vdim, kv_rank, heads * kv_rank, kv_rank, kv_rank, vdim * kv_rank,
                           heads * vdim, vdim)
+
+    def latent_finish(self, proj, cq, q_norm_w, kv_norm_w, eps, freq, rot_dim, rot_dims, batch, block_table, kv_cache,
+                      kv_layer, page_size, q_rank, kv_rank) -> None:
+        """csrc/latent.cu: the float32 rows [q latent | kv latent | rotated key part] -> normed query latents ``cq`` and,
+        with kv_rank > 0, the token's cache slot [normed kv latent | rotated key part]."""
+        self._need_cuda(proj, cq, q_norm_w, kv_norm_w, freq, block_table)
+        T = proj.shape[0]
+        c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
+        clear = 1 if proj.data_ptr() in self._acc_zero else 0
+        self._check(self.lib.tff_latent_finish(
+            _ptr(proj), _c_int(proj.shape[1]), _c_int(clear), _c_int(q_rank), _c_int(kv_rank), _c_int(rot_dim),
+            _c_int(rot_dims), _ptr(q_norm_w), _ptr(kv_norm_w), _c_float(eps), _ptr(freq), _ptr(batch.positions),
+            _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]), c_ptr if kv_rank > 0 else _vp(0),
+            ctypes.c_longlong(page_stride), _c_int(page_size), _c_int(kv_cache.shape[-1]), _ptr(cq), _c_int(_dt(cq)),
+            _c_int(T), self._stream()), "latent_finish")
+        if clear:
+            self._acc_zero[proj.data_ptr()] = True
+        self.launches += 1
+
+    def latent_q_rot(self, q, q_lat, freq, batch, heads, dim, rot_dim, rot_dims, kv_rank) -> None:
+        """The rotated part of every query head of the rows ``q`` into its place in ``q_lat`` (same type)."""
+        assert q.dtype == q_lat.dtype
+        self._check(self.lib.tff_latent_q_rot(_ptr(q), _c_int(dim), _c_int(rot_dim), _c_int(rot_dims), _ptr(freq),
+                                              _ptr(batch.positions), _ptr(q_lat), _c_int(_dt(q_lat)), _c_int(kv_rank),
+                                              _c_int(heads), _c_int(q.shape[0]), self._stream()), "latent_q_rot")
+        self.launches += 1
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
         """table float32 [max_pos, rot_dim/2, 2] = (cos, sin)(pos * theta^(-2i/rot_dim)).

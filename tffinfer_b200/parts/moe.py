@@ -8,7 +8,7 @@ token uses ``top``.
     weight_on "output":  out = sum_e w_e down_e( act(gate_e(h)) * up_e(h) )
 
 The experts' tensors are ``<prefix>.e<i>.{gate,up,down}`` and the router ``<prefix>.router`` unless ``names`` says
-otherwise; they are stacked into [E, ff, hidden] / [E, hidden, ff] when loaded, and the tokens of a step are sorted
+otherwise; they are stacked into [E, 2 ff, hidden] (gate and up) and [E, hidden, ff] when loaded, and the tokens of a step are sorted
 by expert on the device (kernels/library.py ``routed_mlp``): nothing of it waits for the host."""
 from __future__ import annotations
 
@@ -38,7 +38,8 @@ class RoutedExperts(FeedForward):
         self.activation, self.renormalize, self.weight_on = activation, bool(renormalize), weight_on
         self.names = {"router": "router", "expert": "e{}", "gate": "gate", "up": "up", "down": "down"}
         self.names.update(names or {})
-        self.w_router = self.w_gate = self.w_up = self.w_down = None
+        self.w_router = self.w_gate_up = self.w_down = None
+        self.gate_up_layout = "blocked"
 
     def _expert(self, e: int, which: str) -> str:
         return f"{self.names['expert'].format(e)}.{self.names[which]}"
@@ -52,19 +53,20 @@ class RoutedExperts(FeedForward):
         return s
 
     def load(self, tensors, ops, act_dtype) -> None:
-        def stack(which):
-            ts = [tensors[self._expert(e, which)] for e in range(self.num_experts)]
-            dt = ts[0].dtype if all(t.dtype == ts[0].dtype for t in ts) else torch.float32
-            return torch.stack([t.to(dt) for t in ts], dim=0).contiguous()
+        def all_of(*which):
+            ts = [[tensors[self._expert(e, w)] for e in range(self.num_experts)] for w in which]
+            same = all(t.dtype == ts[0][0].dtype for l in ts for t in l)
+            return [[t if same else t.to(torch.float32) for t in l] for l in ts]
         self.w_router = tensors[self.names["router"]]
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
-        if self.w_up.dtype != self.w_gate.dtype:
-            self.w_gate, self.w_up = self.w_gate.float(), self.w_up.float()
+        gates, ups = all_of("gate", "up")
+        # one tensor for gate and up of all experts; the kernel library chooses how their rows are laid out
+        self.w_gate_up, self.gate_up_layout = ops.stack_gate_up(gates, ups)
+        self.w_down = torch.stack(all_of("down")[0], dim=0).contiguous()
 
     def forward(self, h, ctx, residual):
         out = None
         if residual is None:
             out = torch.empty((h.shape[0], self.hidden_size), dtype=torch.float32, device=h.device)
-        ctx.ops.routed_mlp(h, self.w_router, self.w_gate, self.w_up, self.w_down, residual, self.top, self.renormalize,
+        ctx.ops.routed_mlp(h, self.w_router, self.w_gate_up, self.gate_up_layout, self.w_down, residual, self.top, self.renormalize,
                            self.weight_on, self.activation, out=out)
         return residual if residual is not None else out
