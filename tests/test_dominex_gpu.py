@@ -146,7 +146,7 @@ def _select(rows, cols, at):
     return w
 
 
-def _chunk_case(ops, dtype, H, G, d, dv, chunk, window, lens, starts, aim, biased, page=8):
+def _chunk_case(ops, dtype, H, G, d, dv, chunk, window, lens, starts, aim, biased, page=8, splits=None):
     """Requests whose step brings lens[b] tokens after starts[b] cached ones; in every request a key is planted at
     distance aim[b] behind the LAST query (its query and that key are scaled so that their score stands out among all
     others) with a value of its own: whether it is seen decides the output."""
@@ -191,7 +191,7 @@ def _chunk_case(ops, dtype, H, G, d, dv, chunk, window, lens, starts, aim, biase
     out = torch.full((qd.shape[0], nq * dv + 3), float("nan"), dtype=dt, device=dev)
     f32 = lambda t: None if t is None else t.float().to(dev)
     ops.attention_tile(qd, step, step.block_table, cache, 0, page, out, nq, H, d, dv, 0.25, window=window, chunk=chunk,
-                       temp=f32(temp), r1=f32(r1), r2=f32(r2), out_scale=0.5, out_off=3)
+                       temp=f32(temp), r1=f32(r1), r2=f32(r2), out_scale=0.5, out_off=3, num_splits=splits)
     torch.cuda.synchronize()
     got = out[:, 3:].double().cpu() * 2.0
     want = torch.cat(want)
@@ -216,6 +216,10 @@ def test_chunk_attention_edges_and_far_keys(ops, dtype, lens, starts):
     _chunk_case(ops, dtype, 2, 1, 32, 8, 0, 10, lens, starts, [9] * len(lens), biased=False)         # a window's last key
     _chunk_case(ops, dtype, 2, 1, 32, 8, 0, 10, lens, starts, [10] * len(lens), biased=False)        # ... and the one beyond
     _chunk_case(ops, dtype, 2, 2, 8, 8, 5, 3, lens, starts, [2] * len(lens), biased=True)            # both at once
+    # the key range in shares (more shares than some rows have key blocks), merged afterwards
+    for splits in (2, 8):
+        _chunk_case(ops, dtype, 1, 4, 16, 16, 0, 0, lens, starts, [e for e in ends], biased=True, splits=splits)
+        _chunk_case(ops, dtype, 2, 3, 24, 40, 64, 0, lens, starts, [e % 64 for e in ends], biased=True, splits=splits)
 
 
 @pytest.mark.parametrize("width", [8, 100, 300])
@@ -224,7 +228,7 @@ def test_min_gru_steps_and_slots(ops, width):
     against the plain recurrence over the whole sequences; output columns and scale as the caller says."""
     dev = "cuda"
     g = torch.Generator().manual_seed(2)
-    lens1, lens2 = [5, 1, 33], [1, 1, 1]
+    lens1, lens2 = [5, 1, 200], [1, 1, 1]          # 200: the chunked passes, with a last chunk that is not full
     slots = [3, 0, 2]
     state = torch.full((5, width), float("nan"), device=dev)
     bz, bx = torch.randn(width, generator=g), torch.randn(width, generator=g)

@@ -30,6 +30,7 @@ struct TileArgs {
     float scale; int window, chunk;
     const float* temp; const float* r1; const float* r2;
     float out_scale; int q_ld, out_ld, out_off;
+    int splits; float* part_o; float* part_ml;     // splits > 1: shares of the key range, merged by a second kernel
 };
 
 template <typename TQ, typename TC, int NC>
@@ -51,7 +52,8 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int t0 = a.q_start[b], q_len = a.q_start[b + 1] - t0, pos0 = a.pos_start[b];
-    const int n_rows = q_len * G, r0 = blockIdx.x * ROWS;
+    const int split = blockIdx.x % a.splits;
+    const int n_rows = q_len * G, r0 = (blockIdx.x / a.splits) * ROWS;
     if (r0 >= n_rows) return;
     pdl_wait();
 
@@ -94,7 +96,11 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
     for (int i = 0; i < 4; ++i) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
     const int* table = a.block_table + (size_t)b * a.table_width;
 
-    for (int k0 = (lo_min / KB) * KB; k0 <= p_max; k0 += KB) {
+    // the tile's key blocks, in equal contiguous shares when the key range is cut (a share may be empty)
+    const int kb_first = lo_min / KB, kb_count = p_max / KB - kb_first + 1;
+    const int kb_lo = kb_first + (int)((long long)kb_count * split / a.splits);
+    const int kb_hi = kb_first + (int)((long long)kb_count * (split + 1) / a.splits);
+    for (int k0 = kb_lo * KB; k0 < kb_hi * KB; k0 += KB) {
         // the block's keys (and values) into shared memory as float32; keys outside [lo_min, p_max] are zeros
         for (int kk = warp; kk < KB; kk += THREADS / 32) {
             const int n = k0 + kk;
@@ -113,11 +119,13 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
             float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
             const float* qa = Qs + ra * d; const float* qb = Qs + rb * d;
             const float* ka = Ks + kx * kstride; const float* kb = Ks + (kx + 16) * kstride;
+            if (pa >= 0) {                                      // rows rise in pairs: no first row, no second either
 #pragma unroll 4
-            for (int i = 0; i < d; ++i) {
-                const float x0 = qa[i], x1 = qb[i], y0 = ka[i], y1 = kb[i];
-                s00 = fmaf(x0, y0, s00); s01 = fmaf(x0, y1, s01);
-                s10 = fmaf(x1, y0, s10); s11 = fmaf(x1, y1, s11);
+                for (int i = 0; i < d; ++i) {
+                    const float x0 = qa[i], x1 = qb[i], y0 = ka[i], y1 = kb[i];
+                    s00 = fmaf(x0, y0, s00); s01 = fmaf(x0, y1, s01);
+                    s10 = fmaf(x1, y0, s10); s11 = fmaf(x1, y1, s11);
+                }
             }
             const int n0 = k0 + kx, n1 = k0 + kx + 16;
             auto score = [&](float dot, float sc, float r1, float r2, int p, int lo, int n) -> float {
@@ -154,7 +162,7 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
             for (int j = 0; j < NC; ++j) { oa[j] *= al_a; ob[j] *= al_b; }
             const float* vbase = own_v ? Vs : Ks;
             const int vstride = own_v ? dv : kstride;
-            for (int kk = 0; kk < KB; ++kk) {
+            for (int kk = 0; kk < KB && pa >= 0; ++kk) {
                 const float p0 = Ps[ra * (KB + 1) + kk], p1 = Ps[rb * (KB + 1) + kk];
                 const float* v = vbase + kk * vstride;
 #pragma unroll
@@ -169,28 +177,68 @@ attention_tile_kernel(const TQ* __restrict__ q, const TC* __restrict__ cache, TQ
         }
         __syncthreads();
     }
-    // the rows' sums live in the softmax warps: hand them over through shared memory
+    // the rows' sums (and maxima) live in the softmax warps: hand them over through shared memory
+    float* m_s = Ps;                                            // the scores' buffer is free now
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-        if (lane == 0) alpha_s[warp * 4 + i] = l_run[i];
+        if (lane == 0) { alpha_s[warp * 4 + i] = l_run[i]; m_s[warp * 4 + i] = m_run[i]; }
     __syncthreads();
 #pragma unroll
     for (int side = 0; side < 2; ++side) {
         const int rr = side ? rb : ra, r = r0 + rr;
         if (r >= n_rows) continue;
-        const float inv = a.out_scale / alpha_s[rr];
-        TQ* orow = out + (size_t)(t0 + r / G) * a.out_ld + a.out_off + (size_t)(kvh * G + r % G) * dv;
+        const int t = t0 + r / G, h = kvh * G + r % G;
+        if (a.splits == 1) {
+            const float inv = a.out_scale / alpha_s[rr];
+            TQ* orow = out + (size_t)t * a.out_ld + a.out_off + (size_t)h * dv;
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-            const int c = cx + 16 * j;
-            if (c < dv) orow[c] = from_f32<TQ>((side ? ob[j] : oa[j]) * inv);
+            for (int j = 0; j < NC; ++j) {
+                const int c = cx + 16 * j;
+                if (c < dv) orow[c] = from_f32<TQ>((side ? ob[j] : oa[j]) * inv);
+            }
+        } else {                                                // this share's unnormalised sums, its maximum and its sum
+            const size_t slot = ((size_t)t * a.nq + h) * a.splits + split;
+            float* prow = a.part_o + slot * dv;
+#pragma unroll
+            for (int j = 0; j < NC; ++j) {
+                const int c = cx + 16 * j;
+                if (c < dv) prow[c] = side ? ob[j] : oa[j];
+            }
+            if (cx == 0) { a.part_ml[2 * slot] = m_s[rr]; a.part_ml[2 * slot + 1] = alpha_s[rr]; }
         }
+    }
+}
+
+// out[t, h] = out_scale * sum_s w_s o_s / sum_s w_s l_s with w_s = exp(m_s - max m): one warp per (token, head)
+template <typename TQ>
+__global__ void __launch_bounds__(128)
+attention_tile_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, TQ* __restrict__ out,
+                            int out_ld, int out_off, long long rows, int nq, int dv, int splits, float out_scale) {
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    pdl_wait();
+    const float* ml = part_ml + (size_t)row * splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += (ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M)) * ml[2 * s + 1];
+    const float inv = out_scale / L;
+    TQ* orow = out + (size_t)(row / nq) * out_ld + out_off + (size_t)(row % nq) * dv;
+    for (int c = lane; c < dv; c += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float w = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M);
+            if (w != 0.f) acc = fmaf(w, part_o[((size_t)row * splits + s) * dv + c], acc);
+        }
+        orow[c] = from_f32<TQ>(acc * inv);
     }
 }
 
 template <typename TQ, typename TC>
 int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, int num_requests, int max_q_len,
-                cudaStream_t stream) {
+                int num_tokens, cudaStream_t stream) {
     const int G = a.nq / a.nkv;
     const int tiles = (max_q_len * G + ROWS - 1) / ROWS;
     if (num_requests > 65535 || a.nkv > 65535) return TFF_ERR_UNSUPPORTED;
@@ -198,13 +246,18 @@ int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, 
     const size_t smem = sizeof(float) * ((size_t)ROWS * a.d + (size_t)KB * (a.d + 1) + (own_v ? (size_t)KB * a.dv : 0) +
                                          (size_t)ROWS * (KB + 1) + ROWS) + sizeof(int) * 2 * ROWS;
     if (smem > 220 * 1024) return TFF_ERR_UNSUPPORTED;
-    dim3 grid(tiles, a.nkv, num_requests);
+    dim3 grid(tiles * a.splits, a.nkv, num_requests);
 #define TFF_TILE(NCV)                                                                                                \
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(attention_tile_kernel<TQ, TC, NCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        return tff_launch_pdl(attention_tile_kernel<TQ, TC, NCV>, grid, dim3(THREADS), smem, stream, (const TQ*)q,   \
-                              (const TC*)cache, (TQ*)out, a);                                                        \
+        const int st = tff_launch_pdl(attention_tile_kernel<TQ, TC, NCV>, grid, dim3(THREADS), smem, stream, (const TQ*)q, \
+                                      (const TC*)cache, (TQ*)out, a);                                                \
+        if (st != TFF_OK || a.splits == 1) return st;                                                                \
+        const long long rows = (long long)num_tokens * a.nq;                                                         \
+        return tff_launch_pdl(attention_tile_merge_kernel<TQ>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream, \
+                              (const float*)a.part_o, (const float*)a.part_ml, (TQ*)out, a.out_ld, a.out_off, rows,  \
+                              a.nq, a.dv, a.splits, a.out_scale);                                                    \
     } while (0)
     if (a.dv <= 64) TFF_TILE(4);
     if (a.dv <= 128) TFF_TILE(8);
@@ -219,12 +272,15 @@ int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, 
 
 // q [tokens, q_ld] with head h at columns h*d; the cache pointer is the start of the layer's share of the pool (the
 // layer's offset already added); ``planes`` 2: values in the second plane of a page, 1: the value is the first dv
-// elements of the key's slot.  is_bf16: q, out and the cache are bfloat16, else float32.
+// elements of the key's slot.  is_bf16: q, out and the cache are bfloat16, else float32.  splits > 1: every tile's key
+// range in that many shares (float32 workspaces part_o [tokens*nq, splits, dv] and part_ml [tokens*nq, splits, 2]) and a
+// merge kernel; for steps of few rows behind long contexts, which would otherwise be a handful of CTAs.
 TFF_API int tff_attention_tile(
     const void* q, int is_bf16, int q_ld, const int* q_start, const int* pos_start, const int* block_table,
     int table_width, const void* cache, long long page_stride, int planes, int page_size, int slot,
     void* out, int out_ld, int out_off, int num_requests, int max_q_len, int nq, int nkv, int d, int dv, float scale,
-    int window, int chunk, const float* temp, const float* r1, const float* r2, float out_scale, cudaStream_t stream) {
+    int window, int chunk, const float* temp, const float* r1, const float* r2, float out_scale,
+    int num_tokens, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
     if (num_requests <= 0 || max_q_len <= 0) return TFF_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || dv <= 0 || slot < d || page_size <= 0 || window < 0 || chunk < 0 ||
         (planes != 1 && planes != 2) || (planes == 2 && slot < dv) || (planes == 1 && dv > d) || ((r1 == nullptr) != (r2 == nullptr)))
@@ -236,6 +292,8 @@ TFF_API int tff_attention_tile(
     a.slot = slot; a.page_size = page_size; a.nq = nq; a.nkv = nkv; a.d = d; a.dv = dv; a.scale = scale;
     a.window = window; a.chunk = chunk; a.temp = temp; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     a.q_ld = q_ld; a.out_ld = out_ld; a.out_off = out_off;
-    if (is_bf16) return launch_tile<bf16, bf16>(q, cache, out, a, num_requests, max_q_len, stream);
-    return launch_tile<float, float>(q, cache, out, a, num_requests, max_q_len, stream);
+    if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return TFF_ERR_BAD_ARGUMENT;
+    a.splits = splits; a.part_o = part_o; a.part_ml = part_ml;
+    if (is_bf16) return launch_tile<bf16, bf16>(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
+    return launch_tile<float, float>(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
 }

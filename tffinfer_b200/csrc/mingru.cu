@@ -38,7 +38,107 @@ min_gru_kernel(float* __restrict__ proj, int ld, int z_off, int x_off, int g_off
     *sp = S;
 }
 
+// The same recurrence for long portions, in chunks of CHUNK tokens of a request that are worked on side by side.  With
+// a_t = 1 - z_t and b_t = z_t c_t the recurrence is S_t = a_t S_(t-1) + b_t, so a chunk maps its incoming state to
+// A S + B with A = prod a_t and B = the chunk run from zero:
+//   pass 0   per (request, chunk, channel): A and B
+//   pass 1   per (request, channel): over the chunks in order, the state each chunk starts from; the last into the slot
+//   pass 2   per (request, chunk, channel): the chunk again, token by token from its incoming state, writing the outputs
+constexpr int CHUNK = 64;
+
+__device__ __forceinline__ void gru_gates(float zr, float xr, float bzc, float bxc, float& a, float& bb) {
+    const float z = 1.0f / (1.0f + expf(-(zr + bzc)));
+    const float u = xr + bxc;
+    const float cand = u >= 0.f ? u + 0.5f : 1.0f / (1.0f + expf(-u));
+    a = 1.0f - z; bb = z * cand;
+}
+
+template <typename TO, int PASS>
+__global__ void __launch_bounds__(128)
+min_gru_chunk_kernel(float* __restrict__ proj, int ld, int z_off, int x_off, int g_off, int clear_input,
+                     const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
+                     const int* __restrict__ q_start, const int* __restrict__ slots, int width, int max_chunks,
+                     float* __restrict__ wsA, float* __restrict__ wsB, float* __restrict__ wsS,
+                     TO* __restrict__ out, int out_ld, int out_off, float out_scale) {
+    pdl_launch_dependents();
+    const int c = blockIdx.x * 128 + threadIdx.x, b = blockIdx.z;
+    if (c >= width) return;
+    const float bzc = bz ? bz[c] : 0.f, bxc = bx ? bx[c] : 0.f;
+    pdl_wait();
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const int chunks = (t1 - t0 + CHUNK - 1) / CHUNK;
+    if (PASS == 1) {
+        float* sp = state + (size_t)slots[b] * width + c;
+        float S = *sp;
+        for (int k = 0; k < chunks; ++k) {
+            const size_t at = ((size_t)b * max_chunks + k) * width + c;
+            wsS[at] = S;
+            S = wsA[at] * S + wsB[at];
+        }
+        *sp = S;
+        return;
+    }
+    const int k = blockIdx.y;
+    if (k >= chunks) return;
+    const size_t at = ((size_t)b * max_chunks + k) * width + c;
+    const int ta = t0 + k * CHUNK, tb = min(ta + CHUNK, t1);
+    if (PASS == 0) {
+        float A = 1.f, B = 0.f;
+        for (int t = ta; t < tb; ++t) {
+            const float* row = proj + (size_t)t * ld;
+            float a, bb;
+            gru_gates(row[z_off + c], row[x_off + c], bzc, bxc, a, bb);
+            A *= a; B = a * B + bb;
+        }
+        wsA[at] = A; wsB[at] = B;
+    } else {
+        float S = wsS[at];
+        for (int t = ta; t < tb; ++t) {
+            float* row = proj + (size_t)t * ld;
+            const float zr = row[z_off + c], xr = row[x_off + c], gr = row[g_off + c];
+            if (clear_input) { row[z_off + c] = 0.f; row[x_off + c] = 0.f; row[g_off + c] = 0.f; }
+            float a, bb;
+            gru_gates(zr, xr, bzc, bxc, a, bb);
+            S = a * S + bb;
+            out[(size_t)t * out_ld + out_off + c] = from_f32<TO>(out_scale * S * (gr / (1.0f + expf(-gr))));
+        }
+    }
+}
+
 }  // namespace
+
+// Floats of workspace the chunked form needs for a step whose longest portion has max_q_len tokens.
+TFF_API long long tff_min_gru_workspace(int num_requests, int max_q_len, int width) {
+    return 3LL * num_requests * ((max_q_len + CHUNK - 1) / CHUNK) * width;
+}
+
+TFF_API int tff_min_gru_chunked(float* proj, int ld, int z_off, int x_off, int g_off, int clear_input, const float* bz,
+                                const float* bx, float* state, int num_slots, const int* q_start, const int* slots,
+                                int num_requests, int max_q_len, int width, float* workspace, void* out, int out_dt,
+                                int out_ld, int out_off, float out_scale, cudaStream_t stream) {
+    if (num_requests <= 0 || max_q_len <= 0) return TFF_OK;
+    if (!proj || !state || !q_start || !slots || !out || !workspace || width <= 0 || num_slots <= 0) return TFF_ERR_BAD_ARGUMENT;
+    const int max_chunks = (max_q_len + CHUNK - 1) / CHUNK;
+    if (num_requests > 65535 || max_chunks > 65535) return TFF_ERR_UNSUPPORTED;
+    float* wsA = workspace;
+    float* wsB = wsA + (size_t)num_requests * max_chunks * width;
+    float* wsS = wsB + (size_t)num_requests * max_chunks * width;
+    dim3 grid((width + 127) / 128, max_chunks, num_requests), grid1((width + 127) / 128, 1, num_requests);
+#define TFF_GRU(TO)                                                                                                      \
+    do {                                                                                                                 \
+        int st = tff_launch_pdl(min_gru_chunk_kernel<TO, 0>, grid, dim3(128), 0, stream, proj, ld, z_off, x_off, g_off, 0, bz, bx, \
+                                state, q_start, slots, width, max_chunks, wsA, wsB, wsS, (TO*)out, out_ld, out_off, out_scale); \
+        if (st != TFF_OK) return st;                                                                                     \
+        st = tff_launch_pdl(min_gru_chunk_kernel<TO, 1>, grid1, dim3(128), 0, stream, proj, ld, z_off, x_off, g_off, 0, bz, bx, \
+                            state, q_start, slots, width, max_chunks, wsA, wsB, wsS, (TO*)out, out_ld, out_off, out_scale); \
+        if (st != TFF_OK) return st;                                                                                     \
+        return tff_launch_pdl(min_gru_chunk_kernel<TO, 2>, grid, dim3(128), 0, stream, proj, ld, z_off, x_off, g_off, clear_input, \
+                              bz, bx, state, q_start, slots, width, max_chunks, wsA, wsB, wsS, (TO*)out, out_ld, out_off, out_scale); \
+    } while (0)
+    if (out_dt == 0) TFF_GRU(float);
+    TFF_GRU(bf16);
+#undef TFF_GRU
+}
 
 TFF_API int tff_min_gru(float* proj, int ld, int z_off, int x_off, int g_off, int clear_input, const float* bz,
                         const float* bx, float* state, int num_slots, const int* q_start, const int* slots,

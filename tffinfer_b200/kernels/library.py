@@ -662,7 +662,7 @@ class CudaKernels:
 
     def attention_tile(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
                        window: int = 0, chunk: int = 0, temp=None, r1=None, r2=None, out_scale: float = 1.0,
-                       out_off: int = 0) -> None:
+                       out_off: int = 0, num_splits=None) -> None:
         """q [T, nq*d] against the paged cache -> columns out_off .. out_off + nq*dv of ``out`` (times out_scale), in
         float32 arithmetic whatever the storage type.  The cache has two planes (keys, values) or one (the value
         of a token is the first dv elements of its key).  Visibility: causal, within ``window`` keys, within the
@@ -676,13 +676,32 @@ class CudaKernels:
         for v in (temp, r1, r2):
             assert v is None or (v.dtype == torch.float32 and v.numel() == nq)
         c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
+        splits = self.tile_splits(batch, nq, nkv, window, chunk) if num_splits is None else int(num_splits)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty(T * nq * splits * dv, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(T * nq * splits * 2, dtype=torch.float32, device=q.device)
         self._check(self.lib.tff_attention_tile(
             _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(block_table),
             _c_int(block_table.shape[1]), c_ptr, ctypes.c_longlong(page_stride), _c_int(planes), _c_int(page_size),
             _c_int(slot), _ptr(out), _c_int(out.shape[1]), _c_int(out_off), _c_int(batch.num_requests),
             _c_int(batch.max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_float(scale), _c_int(window),
-            _c_int(chunk), _ptr(temp), _ptr(r1), _ptr(r2), _c_float(out_scale), self._stream()), "attention_tile")
-        self.launches += 1
+            _c_int(chunk), _ptr(temp), _ptr(r1), _ptr(r2), _c_float(out_scale), _c_int(T), _c_int(splits), _ptr(part_o),
+            _ptr(part_ml), self._stream()), "attention_tile")
+        self.launches += 2 if splits > 1 else 1
+
+    def tile_splits(self, batch, nq: int, nkv: int, window: int = 0, chunk: int = 0) -> int:
+        """In how many shares attention_tile cuts every tile's key range: a power of two such that a step of few rows
+        behind long contexts (decoded tokens above all) still gives every SM two CTAs, with at least four key blocks
+        of 32 a share."""
+        tiles = -(-(batch.max_q_len * (nq // nkv)) // 32)
+        ctas = tiles * nkv * batch.num_requests
+        span = min([s for s in (window, chunk) if s > 0] + [int(batch.max_kv_len)])
+        blocks = -(-span // 32)
+        splits = 1
+        while splits < 32 and ctas * splits * 2 <= 2 * self.NUM_SMS and splits * 2 * 4 <= blocks:
+            splits *= 2
+        return splits
 
     # ------------------------------------------------------- many small products in one launch
     def gemm_grouped(self, a, b, c, groups: int, M: int, N: int, K: int, lda: int, a_gs: int, ldb: int, b_gs: int,
@@ -826,14 +845,28 @@ class CudaKernels:
         for v in (bz, bx):
             assert v is None or (v.dtype == torch.float32 and v.numel() == width)
         clear = 1 if proj.data_ptr() in self._acc_zero else 0
-        self._check(self.lib.tff_min_gru(_ptr(proj), _c_int(proj.shape[1]), _c_int(z_off), _c_int(x_off), _c_int(g_off),
-                                         _c_int(clear), _ptr(bz), _ptr(bx), _ptr(state), _c_int(state.shape[0]),
-                                         _ptr(batch.q_start), _ptr(batch.slots), _c_int(batch.num_requests), _c_int(width),
-                                         _ptr(out), _c_int(_dt(out)), _c_int(out.shape[1]), _c_int(out_off),
-                                         _c_float(out_scale), self._stream()), "min_gru")
+        if batch.max_q_len > self.GRU_CHUNKED_FROM:
+            # long portions: chunks of a request side by side (three passes), not one thread walking thousands of tokens
+            self.lib.tff_min_gru_workspace.restype = ctypes.c_longlong
+            need = int(self.lib.tff_min_gru_workspace(_c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(width)))
+            ws = torch.empty(need, dtype=torch.float32, device=proj.device)
+            self._check(self.lib.tff_min_gru_chunked(
+                _ptr(proj), _c_int(proj.shape[1]), _c_int(z_off), _c_int(x_off), _c_int(g_off), _c_int(clear), _ptr(bz),
+                _ptr(bx), _ptr(state), _c_int(state.shape[0]), _ptr(batch.q_start), _ptr(batch.slots),
+                _c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(width), _ptr(ws), _ptr(out), _c_int(_dt(out)),
+                _c_int(out.shape[1]), _c_int(out_off), _c_float(out_scale), self._stream()), "min_gru_chunked")
+            self.launches += 3
+        else:
+            self._check(self.lib.tff_min_gru(_ptr(proj), _c_int(proj.shape[1]), _c_int(z_off), _c_int(x_off), _c_int(g_off),
+                                             _c_int(clear), _ptr(bz), _ptr(bx), _ptr(state), _c_int(state.shape[0]),
+                                             _ptr(batch.q_start), _ptr(batch.slots), _c_int(batch.num_requests), _c_int(width),
+                                             _ptr(out), _c_int(_dt(out)), _c_int(out.shape[1]), _c_int(out_off),
+                                             _c_float(out_scale), self._stream()), "min_gru")
+            self.launches += 1
         if clear and last_reader:
             self._acc_zero[proj.data_ptr()] = True
-        self.launches += 1
+
+    GRU_CHUNKED_FROM = 32         # longest portion of a step from which the recurrence runs chunk by chunk
 
     # ------------------------------------------------------- latent attention
     def latent_attend(self, h, w_down, q_norm_w, kv_norm_w, eps: float, w_uq, w_uk_t, w_uv, freq, batch, block_table,
