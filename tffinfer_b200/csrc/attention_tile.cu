@@ -17,6 +17,7 @@
 // is in, on how the prompt was cut or on what else is in the batch.  Keys outside the tile's range are never read
 // (pages behind a window may have been given back).
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -268,6 +269,270 @@ int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, 
     return TFF_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same tiles for bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulation): 64 rows x 64 keys, sixteen
+// warps.  Q and the key block lie in shared memory as bfloat16 rows padded by 16 bytes (ldmatrix without bank
+// conflicts); S = Q K^T by a 4 x 4 grid of warps (16 rows x 16 keys each) goes to shared memory as float32 with scale,
+// distance term and mask applied; the softmax warps (four rows each) keep the running maxima and sums in float32 and
+// leave the probabilities as bfloat16; O += P V by a 4 x 4 grid of warps (16 rows x a quarter of the value columns
+// each), V read through ldmatrix.trans from the key rows themselves (one plane) or from the value block.  Everything
+// the float32 kernel above promises about blocks, masks and shares holds here too.
+constexpr int MROWS = 64, MKB = 64, MTHREADS = 512, PST = MKB + 8, SST = MKB + 4;
+
+__device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct MmaGeom { int dpad, kst, vst; };      // padded key size, elements between key rows and between value rows in shared memory
+
+template <int NT>                            // a warp of the value phase owns 16 rows x NT * 8 columns
+__global__ void __launch_bounds__(MTHREADS)
+attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out, TileArgs a,
+                          MmaGeom gm) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int d = a.d, dv = a.dv, G = a.nq / a.nkv;
+    const bool own_v = a.v_offset != 0;
+    const int kst = gm.kst, vst = gm.vst, dpad = gm.dpad;
+    bf16* Qs = (bf16*)smraw;                                    // [MROWS][kst]
+    bf16* Ks = Qs + MROWS * kst;                                // [MKB][kst]
+    bf16* Vs = own_v ? Ks + MKB * kst : Ks;                     // [MKB][vst]
+    bf16* Pb = own_v ? Vs + MKB * vst : Ks + MKB * kst;         // [MROWS][PST] probabilities
+    float* Ss = (float*)(Pb + MROWS * PST);                     // [MROWS][SST] scores
+    float* alpha_s = Ss + MROWS * SST;                          // [MROWS]
+    float* m_fin = alpha_s + MROWS;                             // [MROWS]
+    int* row_p = (int*)(m_fin + MROWS);
+    int* row_lo = row_p + MROWS;
+
+    pdl_launch_dependents();
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = a.q_start[b], q_len = a.q_start[b + 1] - t0, pos0 = a.pos_start[b];
+    const int split = blockIdx.x % a.splits;
+    const int n_rows = q_len * G, r0 = (blockIdx.x / a.splits) * MROWS;
+    if (r0 >= n_rows) return;
+    pdl_wait();
+
+    if (tid < MROWS) {
+        const int r = r0 + tid;
+        int p = -1, lo = 0;
+        if (r < n_rows) {
+            p = pos0 + r / G;
+            if (a.window > 0) lo = max(lo, p - a.window + 1);
+            if (a.chunk > 0) lo = max(lo, (p / a.chunk) * a.chunk);
+        }
+        row_p[tid] = p; row_lo[tid] = lo;
+    }
+    const int dch = dpad / 8;                                   // 16-byte pieces of a padded key
+    for (int idx = tid; idx < MROWS * dch; idx += MTHREADS) {
+        const int rr = idx / dch, c = (idx % dch) * 8, r = r0 + rr;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows && c < d) v = *(const uint4*)(q + (size_t)(t0 + r / G) * a.q_ld + (size_t)(kvh * G + r % G) * d + c);
+        *(uint4*)(Qs + rr * kst + c) = v;
+    }
+    __syncthreads();
+    const int last = min(r0 + MROWS, n_rows) - 1;
+    const int p_max = pos0 + last / G;
+    const int lo_min = row_lo[0];
+
+    const int rw = warp & 3, cw = warp >> 2;                    // 4 x 4 warps: rows rw*16.., keys cw*16.. / columns cw*NT*8..
+    const int fr = lane >> 2, fc = 2 * (lane & 3);              // a thread's place in an accumulator tile: rows fr, fr+8; columns fc, fc+1
+    const int ra = rw * 16 + fr, rb = ra + 8;
+    const int pa = row_p[ra], pb = row_p[rb], la = row_lo[ra], lb = row_lo[rb];
+    const int ha = kvh * G + (r0 + ra) % G, hb = kvh * G + (r0 + rb) % G;
+    const float sa = a.scale * (a.temp ? a.temp[ha] : 1.f), sb = a.scale * (a.temp ? a.temp[hb] : 1.f);
+    const bool biased = a.r1 != nullptr;
+    const float r1a = biased ? a.r1[ha] : 0.f, r2a = biased ? a.r2[ha] : 0.f;
+    const float r1b = biased ? a.r1[hb] : 0.f, r2b = biased ? a.r2[hb] : 0.f;
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    float m_run[4], l_run[4];                                   // softmax phase: warp w owns rows 4w .. 4w+3
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+    const int* table = a.block_table + (size_t)b * a.table_width;
+    const int vch = own_v ? (vst - 8) / 8 : 0;
+
+    const int kb_first = lo_min / MKB, kb_count = p_max / MKB - kb_first + 1;
+    const int kb_lo = kb_first + (int)((long long)kb_count * split / a.splits);
+    const int kb_hi = kb_first + (int)((long long)kb_count * (split + 1) / a.splits);
+    for (int k0 = kb_lo * MKB; k0 < kb_hi * MKB; k0 += MKB) {
+        for (int kk = warp; kk < MKB; kk += MTHREADS / 32) {
+            const int n = k0 + kk;
+            const bf16* src = nullptr;
+            if (n >= lo_min && n <= p_max) {
+                const int page = table[n / a.page_size];
+                if (page >= 0)
+                    src = cache + (size_t)page * a.page_stride + (size_t)kvh * a.head_stride + (size_t)(n % a.page_size) * a.slot;
+            }
+            for (int c = lane; c < dch; c += 32) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (src && c * 8 < d) v = *(const uint4*)(src + c * 8);
+                *(uint4*)(Ks + kk * kst + c * 8) = v;
+            }
+            for (int c = lane; c < vch; c += 32) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (src && c * 8 < dv) v = *(const uint4*)(src + a.v_offset + c * 8);
+                *(uint4*)(Vs + kk * vst + c * 8) = v;
+            }
+        }
+        __syncthreads();
+        {   // S = Q K^T: rows rw*16 .. +16, keys cw*16 .. +16
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t qa = sm_addr(Qs + (rw * 16 + (lane & 15)) * kst + (lane >> 4) * 8);
+            const uint32_t ka = sm_addr(Ks + (cw * 16 + (lane & 7) + (lane >> 4) * 8) * kst + ((lane >> 3) & 1) * 8);
+            for (int kk = 0; kk < dpad; kk += 16) {
+                uint32_t af[4], bfr[4];
+                ldsm4(af, qa + kk * 2);
+                ldsm4(bfr, ka + kk * 2);
+                mma16816(s0, af, bfr[0], bfr[1]);
+                mma16816(s1, af, bfr[2], bfr[3]);
+            }
+            auto score = [&](float dot, float sc, float r1, float r2, int p, int lo, int n) -> float {
+                if (p < 0 || n > p || n < lo) return -INFINITY;
+                float s = dot * sc;
+                if (biased) s -= r1 * log1pf(r2 * (float)(p - n));
+                return s;
+            };
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c0 = cw * 16 + fc + e, c1 = c0 + 8;
+                Ss[ra * SST + c0] = score(s0[e], sa, r1a, r2a, pa, la, k0 + c0);
+                Ss[rb * SST + c0] = score(s0[2 + e], sb, r1b, r2b, pb, lb, k0 + c0);
+                Ss[ra * SST + c1] = score(s1[e], sa, r1a, r2a, pa, la, k0 + c1);
+                Ss[rb * SST + c1] = score(s1[2 + e], sb, r1b, r2b, pb, lb, k0 + c1);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = warp * 4 + i;
+            const float x0 = Ss[rr * SST + lane], x1 = Ss[rr * SST + lane + 32];
+            const float m_new = fmaxf(m_run[i], warp_max(fmaxf(x0, x1)));
+            float alpha = 1.f, p0 = 0.f, p1 = 0.f;
+            if (m_new != -INFINITY) {
+                alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
+                p0 = expf(x0 - m_new); p1 = expf(x1 - m_new);
+            }
+            l_run[i] = l_run[i] * alpha + warp_sum(p0 + p1);
+            m_run[i] = m_new;
+            Pb[rr * PST + lane] = __float2bfloat16_rn(p0);
+            Pb[rr * PST + lane + 32] = __float2bfloat16_rn(p1);
+            if (lane == 0) alpha_s[rr] = alpha;
+        }
+        __syncthreads();
+        {   // O += P V: rows rw*16 .. +16, columns cw*NT*8 .. + NT*8
+            const float al_a = alpha_s[ra], al_b = alpha_s[rb];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) { o[j][0] *= al_a; o[j][1] *= al_a; o[j][2] *= al_b; o[j][3] *= al_b; }
+            const uint32_t pa_addr = sm_addr(Pb + (rw * 16 + (lane & 15)) * PST + (lane >> 4) * 8);
+            const uint32_t va = sm_addr(Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * vst + cw * NT * 8 + (lane >> 4) * 8);
+#pragma unroll
+            for (int kk = 0; kk < MKB; kk += 16) {
+                uint32_t af[4];
+                ldsm4(af, pa_addr + kk * 2);
+#pragma unroll
+                for (int j2 = 0; j2 < NT / 2; ++j2) {
+                    uint32_t bfr[4];
+                    ldsm4t(bfr, va + (kk * vst + j2 * 16) * 2);
+                    mma16816(o[2 * j2], af, bfr[0], bfr[1]);
+                    mma16816(o[2 * j2 + 1], af, bfr[2], bfr[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (lane == 0) { alpha_s[warp * 4 + i] = l_run[i]; m_fin[warp * 4 + i] = m_run[i]; }
+    __syncthreads();
+#pragma unroll
+    for (int side = 0; side < 2; ++side) {
+        const int rr = side ? rb : ra, r = r0 + rr;
+        if (r >= n_rows) continue;
+        const int t = t0 + r / G, h = kvh * G + r % G;
+        if (a.splits == 1) {
+            const float inv = a.out_scale / alpha_s[rr];
+            bf16* orow = out + (size_t)t * a.out_ld + a.out_off + (size_t)h * dv;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = cw * NT * 8 + j * 8 + fc + e;
+                    if (c < dv) orow[c] = __float2bfloat16_rn(o[j][side * 2 + e] * inv);
+                }
+        } else {
+            const size_t slot = ((size_t)t * a.nq + h) * a.splits + split;
+            float* prow = a.part_o + slot * dv;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int c = cw * NT * 8 + j * 8 + fc + e;
+                    if (c < dv) prow[c] = o[j][side * 2 + e];
+                }
+            if (cw == 0 && fc == 0) { a.part_ml[2 * slot] = m_fin[rr]; a.part_ml[2 * slot + 1] = alpha_s[rr]; }
+        }
+    }
+}
+
+static bool tile_mma_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TFFINFER_TILE_MMA"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v != 0;
+}
+
+// Launches the tensor-core form if the sizes allow it; TFF_ERR_UNSUPPORTED otherwise (the caller takes the float32 form).
+int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs& a, int num_requests, int max_q_len,
+                    int num_tokens, cudaStream_t stream) {
+    const int G = a.nq / a.nkv;
+    const bool own_v = a.v_offset != 0;
+    if (!tile_mma_enabled() || (a.d & 7) || (a.slot & 7) || (a.q_ld & 7) || (a.page_stride & 7) || (a.v_offset & 7) ||
+        ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || (own_v && (a.dv & 7)) || a.dv > 512)
+        return TFF_ERR_UNSUPPORTED;
+    if (num_requests > 65535 || a.nkv > 65535) return TFF_ERR_UNSUPPORTED;
+    int nt = 2;
+    while (nt * 32 < a.dv) nt *= 2;                              // value columns per warp: nt * 8, four warps across
+    MmaGeom gm;
+    gm.dpad = (a.d + 15) / 16 * 16;
+    gm.kst = (own_v ? gm.dpad : max(gm.dpad, nt * 32)) + 8;
+    gm.vst = own_v ? nt * 32 + 8 : gm.kst;
+    const size_t smem = 2 * ((size_t)(MROWS + MKB) * gm.kst + (own_v ? (size_t)MKB * gm.vst : 0) + (size_t)MROWS * PST) +
+                        4 * ((size_t)MROWS * SST + 2 * MROWS) + 4 * 2 * MROWS;
+    if (smem > 220 * 1024) return TFF_ERR_UNSUPPORTED;
+    const int tiles = (max_q_len * G + MROWS - 1) / MROWS;
+    dim3 grid(tiles * a.splits, a.nkv, num_requests);
+#define TFF_TMMA(NTV)                                                                                                \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(attention_tile_mma_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        const int st = tff_launch_pdl(attention_tile_mma_kernel<NTV>, grid, dim3(MTHREADS), smem, stream, (const bf16*)q, \
+                                      (const bf16*)cache, (bf16*)out, a, gm);                                        \
+        if (st != TFF_OK || a.splits == 1) return st;                                                                \
+        const long long rows = (long long)num_tokens * a.nq;                                                         \
+        return tff_launch_pdl(attention_tile_merge_kernel<bf16>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream, \
+                              (const float*)a.part_o, (const float*)a.part_ml, (bf16*)out, a.out_ld, a.out_off, rows, \
+                              a.nq, a.dv, a.splits, a.out_scale);                                                    \
+    } while (0)
+    if (nt == 2) TFF_TMMA(2);
+    if (nt == 4) TFF_TMMA(4);
+    if (nt == 8) TFF_TMMA(8);
+    TFF_TMMA(16);
+#undef TFF_TMMA
+}
+
 }  // namespace
 
 // q [tokens, q_ld] with head h at columns h*d; the cache pointer is the start of the layer's share of the pool (the
@@ -294,6 +559,10 @@ TFF_API int tff_attention_tile(
     a.q_ld = q_ld; a.out_ld = out_ld; a.out_off = out_off;
     if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return TFF_ERR_BAD_ARGUMENT;
     a.splits = splits; a.part_o = part_o; a.part_ml = part_ml;
-    if (is_bf16) return launch_tile<bf16, bf16>(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
+    if (is_bf16) {
+        const int st = launch_tile_mma(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
+        if (st != TFF_ERR_UNSUPPORTED) return st;
+        return launch_tile<bf16, bf16>(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
+    }
     return launch_tile<float, float>(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
 }
