@@ -277,7 +277,7 @@ int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, 
 // leave the probabilities as bfloat16; O += P V by a 4 x 4 grid of warps (16 rows x a quarter of the value columns
 // each), V read through ldmatrix.trans from the key rows themselves (one plane) or from the value block.  Everything
 // the float32 kernel above promises about blocks, masks and shares holds here too.
-constexpr int MROWS = 64, MKB = 64, MTHREADS = 512, PST = MKB + 8, SST = MKB + 4;
+constexpr int MKB = 64, PST = MKB + 8, SST = MKB + 4;
 
 __device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
@@ -296,11 +296,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 
 struct MmaGeom { int dpad, kst, vst; };      // padded key size, elements between key rows and between value rows in shared memory
 
-template <int NT>                            // a warp of the value phase owns 16 rows x NT * 8 columns
-__global__ void __launch_bounds__(MTHREADS)
+// RG groups of 16 rows (a tile has 16 * RG rows and 4 * RG warps: steps of one token need one group, portions four);
+// a warp of the value phase owns 16 rows x NT * 8 columns
+template <int NT, int RG>
+__global__ void __launch_bounds__(128 * RG)
 attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out, TileArgs a,
                           MmaGeom gm) {
     extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int MROWS = 16 * RG, MTHREADS = 128 * RG;
     const int d = a.d, dv = a.dv, G = a.nq / a.nkv;
     const bool own_v = a.v_offset != 0;
     const int kst = gm.kst, vst = gm.vst, dpad = gm.dpad;
@@ -313,6 +316,7 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
     float* m_fin = alpha_s + MROWS;                             // [MROWS]
     int* row_p = (int*)(m_fin + MROWS);
     int* row_lo = row_p + MROWS;
+    const bf16** key_src = (const bf16**)(row_lo + MROWS);     // [MKB] (8-byte aligned: an even number of 4-byte words lies ahead)
 
     pdl_launch_dependents();
     const int b = blockIdx.z, kvh = blockIdx.y;
@@ -345,7 +349,7 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
     const int p_max = pos0 + last / G;
     const int lo_min = row_lo[0];
 
-    const int rw = warp & 3, cw = warp >> 2;                    // 4 x 4 warps: rows rw*16.., keys cw*16.. / columns cw*NT*8..
+    const int rw = warp % RG, cw = warp / RG;                    // 4 x 4 warps: rows rw*16.., keys cw*16.. / columns cw*NT*8..
     const int fr = lane >> 2, fc = 2 * (lane & 3);              // a thread's place in an accumulator tile: rows fr, fr+8; columns fc, fc+1
     const int ra = rw * 16 + fr, rb = ra + 8;
     const int pa = row_p[ra], pb = row_p[rb], la = row_lo[ra], lb = row_lo[rb];
@@ -369,24 +373,31 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
     const int kb_lo = kb_first + (int)((long long)kb_count * split / a.splits);
     const int kb_hi = kb_first + (int)((long long)kb_count * (split + 1) / a.splits);
     for (int k0 = kb_lo * MKB; k0 < kb_hi * MKB; k0 += MKB) {
-        for (int kk = warp; kk < MKB; kk += MTHREADS / 32) {
-            const int n = k0 + kk;
+        // where the block's keys lie (one thread a key), then the rows in 16-byte pieces, all loads independent
+        if (tid < MKB) {
+            const int n = k0 + tid;
             const bf16* src = nullptr;
             if (n >= lo_min && n <= p_max) {
                 const int page = table[n / a.page_size];
                 if (page >= 0)
                     src = cache + (size_t)page * a.page_stride + (size_t)kvh * a.head_stride + (size_t)(n % a.page_size) * a.slot;
             }
-            for (int c = lane; c < dch; c += 32) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (src && c * 8 < d) v = *(const uint4*)(src + c * 8);
-                *(uint4*)(Ks + kk * kst + c * 8) = v;
-            }
-            for (int c = lane; c < vch; c += 32) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (src && c * 8 < dv) v = *(const uint4*)(src + a.v_offset + c * 8);
-                *(uint4*)(Vs + kk * vst + c * 8) = v;
-            }
+            key_src[tid] = src;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < MKB * dch; idx += MTHREADS) {
+            const int kk = idx / dch, c = idx % dch;
+            const bf16* src = key_src[kk];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (src && c * 8 < d) v = *(const uint4*)(src + c * 8);
+            *(uint4*)(Ks + kk * kst + c * 8) = v;
+        }
+        for (int idx = tid; idx < MKB * vch; idx += MTHREADS) {
+            const int kk = idx / vch, c = idx % vch;
+            const bf16* src = key_src[kk];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (src && c * 8 < dv) v = *(const uint4*)(src + a.v_offset + c * 8);
+            *(uint4*)(Vs + kk * vst + c * 8) = v;
         }
         __syncthreads();
         {   // S = Q K^T: rows rw*16 .. +16, keys cw*16 .. +16
@@ -509,16 +520,25 @@ int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs&
     gm.dpad = (a.d + 15) / 16 * 16;
     gm.kst = (own_v ? gm.dpad : max(gm.dpad, nt * 32)) + 8;
     gm.vst = own_v ? nt * 32 + 8 : gm.kst;
+    const int rows_most = max_q_len * G;
+    const int rg = rows_most <= 16 ? 1 : (rows_most <= 32 ? 2 : 4);
+    const int MROWS = 16 * rg;
     const size_t smem = 2 * ((size_t)(MROWS + MKB) * gm.kst + (own_v ? (size_t)MKB * gm.vst : 0) + (size_t)MROWS * PST) +
-                        4 * ((size_t)MROWS * SST + 2 * MROWS) + 4 * 2 * MROWS;
+                        4 * ((size_t)MROWS * SST + 2 * MROWS) + 4 * 2 * MROWS + 8 * MKB;
     if (smem > 220 * 1024) return TFF_ERR_UNSUPPORTED;
-    const int tiles = (max_q_len * G + MROWS - 1) / MROWS;
+    const int tiles = (rows_most + MROWS - 1) / MROWS;
     dim3 grid(tiles * a.splits, a.nkv, num_requests);
 #define TFF_TMMA(NTV)                                                                                                \
     do {                                                                                                             \
+        if (rg == 1) TFF_TMMA_RG(NTV, 1);                                                                            \
+        if (rg == 2) TFF_TMMA_RG(NTV, 2);                                                                            \
+        TFF_TMMA_RG(NTV, 4);                                                                                         \
+    } while (0)
+#define TFF_TMMA_RG(NTV, RGV)                                                                                        \
+    do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
-            cudaFuncSetAttribute(attention_tile_mma_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        const int st = tff_launch_pdl(attention_tile_mma_kernel<NTV>, grid, dim3(MTHREADS), smem, stream, (const bf16*)q, \
+            cudaFuncSetAttribute(attention_tile_mma_kernel<NTV, RGV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        const int st = tff_launch_pdl(attention_tile_mma_kernel<NTV, RGV>, grid, dim3(128 * RGV), smem, stream, (const bf16*)q, \
                                       (const bf16*)cache, (bf16*)out, a, gm);                                        \
         if (st != TFF_OK || a.splits == 1) return st;                                                                \
         const long long rows = (long long)num_tokens * a.nq;                                                         \
@@ -531,6 +551,7 @@ int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs&
     if (nt == 8) TFF_TMMA(8);
     TFF_TMMA(16);
 #undef TFF_TMMA
+#undef TFF_TMMA_RG
 }
 
 }  // namespace

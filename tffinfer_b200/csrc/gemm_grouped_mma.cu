@@ -1,7 +1,7 @@
 // The grouped product of gemm_grouped.cu for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32
 // accumulation): C_g[m, n] = sum_k A_g[m, k] * B_g[n, k], uniform or ragged groups, optional row map, as there.
-// Tiles of 128 x 128 x 32, eight warps of 32 x 64, operands through a three-stage cp.async ring into padded shared
-// memory (rows of 80 bytes: the eight rows of an ldmatrix fall into different banks), fragments by ldmatrix.
+// Tiles of 128 x 128 x 64, eight warps of 32 x 64, operands through a three-stage cp.async ring into padded shared
+// memory (rows of 144 bytes: the eight rows of an ldmatrix fall into different banks), fragments by ldmatrix.
 // Gated form: B_g holds the gate and up rows of a group interleaved in blocks of eight ([g0..g7 | u0..u7 | g8.. ]), so
 // that a thread finds act(gate) and up of the same output element in neighbouring accumulator tiles;
 // C_g[m, f] = act(gate_f) * up_f has half as many columns as B_g has rows.
@@ -12,7 +12,8 @@
 
 namespace {
 
-constexpr int MBM = 128, MBN = 128, MBK = 32, LDS = MBK + 8, STAGES = 3, THREADS = 256;
+constexpr int MBM = 128, MBN = 128, MBK = 64, LDS = MBK + 8, STAGES = 3, THREADS = 256;
+constexpr int CHUNKS = MBK / 8;                          // 16-byte pieces of a tile row
 constexpr int SMEM_BYTES = STAGES * (MBM + MBN) * LDS * 2;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -37,7 +38,7 @@ __device__ __forceinline__ float act_of(float g, int act) {
 }
 
 template <typename TCc, bool GATED>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_gs,
                         const bf16* __restrict__ B, long long ldb, long long b_gs,
                         TCc* __restrict__ C, long long ldc, long long c_gs,
@@ -65,8 +66,8 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
 
     auto load_stage = [&](int s, int k0) {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int c = tid + i * THREADS, r = c >> 2, kc = (c & 3) * 8;
+        for (int i = 0; i < MBM * CHUNKS / THREADS; ++i) {
+            const int c = tid + i * THREADS, r = c / CHUNKS, kc = (c % CHUNKS) * 8;
             const bool ka = k0 + kc < K;
             const bool oka = ka && (m0 + r < m_end);
             cp_async16(smem_addr(As + ((size_t)s * MBM + r) * LDS + kc),
