@@ -82,25 +82,43 @@ min_gru_chunk_kernel(float* __restrict__ proj, int ld, int z_off, int x_off, int
     if (k >= chunks) return;
     const size_t at = ((size_t)b * max_chunks + k) * width + c;
     const int ta = t0 + k * CHUNK, tb = min(ta + CHUNK, t1);
+    // eight tokens' inputs are fetched before any of them is used: the loads of a batch are in flight together
+    constexpr int UN = 8;
     if (PASS == 0) {
         float A = 1.f, B = 0.f;
-        for (int t = ta; t < tb; ++t) {
-            const float* row = proj + (size_t)t * ld;
-            float a, bb;
-            gru_gates(row[z_off + c], row[x_off + c], bzc, bxc, a, bb);
-            A *= a; B = a * B + bb;
+        for (int t = ta; t < tb; t += UN) {
+            float zr[UN], xr[UN];
+#pragma unroll
+            for (int i = 0; i < UN; ++i)
+                if (t + i < tb) { const float* row = proj + (size_t)(t + i) * ld; zr[i] = row[z_off + c]; xr[i] = row[x_off + c]; }
+#pragma unroll
+            for (int i = 0; i < UN; ++i)
+                if (t + i < tb) {
+                    float a, bb;
+                    gru_gates(zr[i], xr[i], bzc, bxc, a, bb);
+                    A *= a; B = a * B + bb;
+                }
         }
         wsA[at] = A; wsB[at] = B;
     } else {
         float S = wsS[at];
-        for (int t = ta; t < tb; ++t) {
-            float* row = proj + (size_t)t * ld;
-            const float zr = row[z_off + c], xr = row[x_off + c], gr = row[g_off + c];
-            if (clear_input) { row[z_off + c] = 0.f; row[x_off + c] = 0.f; row[g_off + c] = 0.f; }
-            float a, bb;
-            gru_gates(zr, xr, bzc, bxc, a, bb);
-            S = a * S + bb;
-            out[(size_t)t * out_ld + out_off + c] = from_f32<TO>(out_scale * S * (gr / (1.0f + expf(-gr))));
+        for (int t = ta; t < tb; t += UN) {
+            float zr[UN], xr[UN], gr[UN];
+#pragma unroll
+            for (int i = 0; i < UN; ++i)
+                if (t + i < tb) {
+                    float* row = proj + (size_t)(t + i) * ld;
+                    zr[i] = row[z_off + c]; xr[i] = row[x_off + c]; gr[i] = row[g_off + c];
+                    if (clear_input) { row[z_off + c] = 0.f; row[x_off + c] = 0.f; row[g_off + c] = 0.f; }
+                }
+#pragma unroll
+            for (int i = 0; i < UN; ++i)
+                if (t + i < tb) {
+                    float a, bb;
+                    gru_gates(zr[i], xr[i], bzc, bxc, a, bb);
+                    S = a * S + bb;
+                    out[(size_t)(t + i) * out_ld + out_off + c] = from_f32<TO>(out_scale * S * (gr[i] / (1.0f + expf(-gr[i]))));
+                }
         }
     }
 }
