@@ -280,6 +280,9 @@ int launch_tile(const void* q, const void* cache, void* out, const TileArgs& a, 
 constexpr int MKB = 64, PST = MKB + 8, SST = MKB + 4;
 
 __device__ __forceinline__ uint32_t sm_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {     // bytes 0: sixteen zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -385,20 +388,22 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
             key_src[tid] = src;
         }
         __syncthreads();
+        // asynchronous 16-byte copies straight into shared memory (zero fill where there is no key or the row has
+        // ended): all of a thread's copies are in flight at once
         for (int idx = tid; idx < MKB * dch; idx += MTHREADS) {
             const int kk = idx / dch, c = idx % dch;
             const bf16* src = key_src[kk];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (src && c * 8 < d) v = *(const uint4*)(src + c * 8);
-            *(uint4*)(Ks + kk * kst + c * 8) = v;
+            const bool ok = src && c * 8 < d;
+            cp_async_16(sm_addr(Ks + kk * kst + c * 8), ok ? (const void*)(src + c * 8) : (const void*)cache, ok ? 16 : 0);
         }
         for (int idx = tid; idx < MKB * vch; idx += MTHREADS) {
             const int kk = idx / vch, c = idx % vch;
             const bf16* src = key_src[kk];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (src && c * 8 < dv) v = *(const uint4*)(src + a.v_offset + c * 8);
-            *(uint4*)(Vs + kk * vst + c * 8) = v;
+            const bool ok = src && c * 8 < dv;
+            cp_async_16(sm_addr(Vs + kk * vst + c * 8), ok ? (const void*)(src + a.v_offset + c * 8) : (const void*)cache, ok ? 16 : 0);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         {   // S = Q K^T: rows rw*16 .. +16, keys cw*16 .. +16
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
