@@ -257,7 +257,7 @@ def test_min_gru_steps_and_slots(ops, width):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,top,ff,W,T", [(5, 1, 24, 40, 70), (7, 3, 64, 128, 130), (3, 3, 10, 52, 9), (1, 1, 16, 64, 3),
-                                           (64, 6, 32, 64, 200), (6, 2, 200, 136, 700)])
+                                           (64, 6, 64, 64, 200), (6, 2, 192, 136, 700), (5, 2, 128, 256, 1500)])
 def test_routed_experts(ops, dtype, E, top, ff, W, T):
     """Route, sort by expert, the two grouped products and the sum, against the plain loop over tokens; the weight on
     the experts' input (as they are) and on their output (renormalised)."""

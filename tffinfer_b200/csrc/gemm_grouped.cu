@@ -63,9 +63,10 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
             if (gk < K) {
                 if (m0 + r < m_end) a = to_f32<TA>(Ag[(size_t)(m0 + r) * lda + gk]);
                 if (n0 + r < N) {
-                    // interleaved: output column n has its gate row at (n / 8) * 16 + n % 8 and its up row 8 further (B2 = B + 8 rows)
+                    // gate and up alternating in blocks of b_interleaved rows: output column n has its gate row at
+                    // (n / blk) * 2 blk + n % blk and its up row blk further (B2 = B + blk rows)
                     const int n = n0 + r;
-                    const size_t brow = b_interleaved ? (size_t)(n >> 3) * 16 + (n & 7) : (size_t)n;
+                    const size_t brow = b_interleaved ? (size_t)(n / b_interleaved) * 2 * b_interleaved + (n % b_interleaved) : (size_t)n;
                     w = to_f32<TB>(Bg[brow * ldb + gk]);
                     if constexpr (GATED) w2 = to_f32<TB>(B2g[brow * ldb + gk]);
                 }
@@ -112,7 +113,8 @@ gemm_grouped_kernel(const TA* __restrict__ A, long long lda, long long a_gs,
 }  // namespace
 
 // dt codes: 0 = float32, 1 = bfloat16.  B2 null = plain product; else gated with ``act`` (0 silu, 1 tanh-gelu).
-// b_interleaved (gated only): the gate and up rows of a group lie interleaved in eights in ONE matrix (B2 = B + 8 rows).
+// b_interleaved (gated only) > 0: the gate and up rows of a group alternate in blocks of that many rows in ONE matrix
+// (B2 = B + that many rows); 0: B and B2 are matrices of their own.
 // Uniform: tile_group null, ``groups`` groups of M rows.  Ragged: the four tile arrays on the device, ``max_tiles`` the
 // grid's size, M unused, c_gs and a_gs usually 0.
 TFF_API int tff_gemm_grouped(

@@ -2,9 +2,10 @@
 // accumulation): C_g[m, n] = sum_k A_g[m, k] * B_g[n, k], uniform or ragged groups, optional row map, as there.
 // Tiles of 128 x 128 x 64, eight warps of 32 x 64, operands through a three-stage cp.async ring into padded shared
 // memory (rows of 144 bytes: the eight rows of an ldmatrix fall into different banks), fragments by ldmatrix.
-// Gated form: B_g holds the gate and up rows of a group interleaved in blocks of eight ([g0..g7 | u0..u7 | g8.. ]), so
-// that a thread finds act(gate) and up of the same output element in neighbouring accumulator tiles;
-// C_g[m, f] = act(gate_f) * up_f has half as many columns as B_g has rows.
+// Gated form: B_g holds the gate and up rows of a group alternating in blocks of 64 ([g0..g63 | u0..u63 | g64.. ], the
+// layout of the tcgen05 products), a tile of 128 rows of B being one such pair of blocks; a warp then takes 32 gate
+// rows and the 32 up rows of the same outputs, so that a thread finds act(gate) and up of an output element four
+// accumulator tiles apart; C_g[m, f] = act(gate_f) * up_f has half as many columns as B_g has rows.
 // Needs K, lda, ldb and the group strides to be multiples of 8 elements and 16-byte aligned bases (the launcher
 // refuses anything else and the caller takes the FMA kernel).  A row's result does not depend on the tile it is in:
 // every output element adds its products in the same order of k.
@@ -106,8 +107,11 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
             for (int mi = 0; mi < 2; ++mi)
                 ldsm4(a[mi], smem_addr(as + (size_t)(wm * 32 + mi * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8));
 #pragma unroll
-            for (int nj = 0; nj < 4; ++nj)
-                ldsm4(b[nj], smem_addr(bs + (size_t)(wn * 64 + nj * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8));
+            for (int nj = 0; nj < 4; ++nj) {
+                // rows of B this warp's 16-row slice nj covers: plain 64 in a row; gated 32 gate rows, then their 32 up rows
+                const int brow = GATED ? ((nj >> 1) * 64 + wn * 32 + (nj & 1) * 16) : (wn * 64 + nj * 16);
+                ldsm4(b[nj], smem_addr(bs + (size_t)(brow + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8));
+            }
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
@@ -129,12 +133,12 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
             TCc* crow = C + (size_t)g * c_gs + (size_t)row * ldc;
             if constexpr (GATED) {
 #pragma unroll
-                for (int nj = 0; nj < 4; ++nj) {
-                    const int f = (n0 + wn * 64 + nj * 16) / 2 + 2 * (lane & 3);
+                for (int t = 0; t < 4; ++t) {
+                    const int f = n0 / 2 + wn * 32 + t * 8 + 2 * (lane & 3);
 #pragma unroll
                     for (int e = 0; e < 2; ++e)
                         if (f + e < N / 2)
-                            crow[f + e] = from_f32<TCc>(act_of(acc[mi][2 * nj][half * 2 + e], act) * acc[mi][2 * nj + 1][half * 2 + e]);
+                            crow[f + e] = from_f32<TCc>(act_of(acc[mi][t][half * 2 + e], act) * acc[mi][t + 4][half * 2 + e]);
                 }
             } else {
 #pragma unroll
@@ -150,7 +154,7 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
 
 }  // namespace
 
-// A and B bfloat16.  gated != 0: B's N rows are gate and up rows interleaved in eights and C has N / 2 columns.
+// A and B bfloat16.  gated != 0: B's N rows are gate and up rows alternating in blocks of 64 and C has N / 2 columns.
 // c_dt 0 = float32, 1 = bfloat16.  The ragged form's tiles must have been planned with tff_gemm_grouped_mma_tile_rows().
 TFF_API int tff_gemm_grouped_mma(
     const void* A, long long lda, long long a_gs, const void* B, long long ldb, long long b_gs,
@@ -159,7 +163,7 @@ TFF_API int tff_gemm_grouped_mma(
     const int* row_map, int groups, int M, int N, int K, int gated, int act, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || !A || !B || !C) return TFF_ERR_BAD_ARGUMENT;
     if ((K & 7) || (lda & 7) || (ldb & 7) || (a_gs & 7) || (b_gs & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) ||
-        (gated && (N & 15)))
+        (gated && (N & 127)))
         return TFF_ERR_UNSUPPORTED;
     dim3 grid;
     if (tile_group) {

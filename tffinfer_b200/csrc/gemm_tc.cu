@@ -61,7 +61,12 @@ __global__ void __launch_bounds__(NUM_THREADS, TileCfg<BN, TMA_OUT, SWAP>::kCtas
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose rows land on TMEM lanes (box 64 x 128)
                const __grid_constant__ CUtensorMap tm_col,    // operand whose rows land on TMEM columns (box 64 x BN)
                const __grid_constant__ CUtensorMap tm_out,    // output, boxes of 128 bytes x 32 rows (TMA_OUT only)
-               TC* __restrict__ out, int rows_lane, int rows_col, int K, int ldo, int stream_k, int* error_flag) {
+               TC* __restrict__ out, int rows_lane, int rows_col, int K, int ldo, int stream_k, int* error_flag,
+               const int* __restrict__ lane_group, int group_rows) {
+    // lane_group (normal orientation only; null: one product): the 128-row tile t of the lane operand belongs to group
+    // lane_group[t] and is multiplied with rows [g * group_rows, (g + 1) * group_rows) of the column operand; a tile of
+    // group -1 is skipped by all three roles.  The table is written by a kernel ahead: read it behind pdl_wait.
+    const bool grouped = lane_group != nullptr;
     using Cfg = TileCfg<BN, TMA_OUT, SWAP>;
     using SegIter = typename std::conditional<SWAP, SegIterShares, SegIterSlices>::type;
     constexpr int STAGES = Cfg::kStages;
@@ -113,10 +118,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
             const uint32_t x_off = SWAP ? (uint32_t)(BM * BK * 2) : 0u;
             int pre_k[STAGES], pre_wrow[STAGES], pre_xrow[STAGES];
             int pre = 0;
+            if (grouped) pdl_wait();
             {
                 SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
                 while (pre < STAGES && it.next()) {
-                    const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN;
+                    int goff = 0;
+                    if (grouped) { const int g = lane_group[it.tile % n_lane_tiles]; if (g < 0) continue; goff = g * group_rows; }
+                    const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN + goff;
                     for (int kb = it.kb0; kb < it.kb1 && pre < STAGES; ++kb, ++pre) {
                         pre_k[pre] = kb * BK;
                         pre_wrow[pre] = SWAP ? lrow : crow;
@@ -135,7 +143,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
             uint32_t n = 0;
             bool ok = true;
             while (ok && it.next()) {
-                const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN;
+                int goff = 0;
+                if (grouped) { const int g = lane_group[it.tile % n_lane_tiles]; if (g < 0) continue; goff = g * group_rows; }
+                const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN + goff;
                 for (int kb = it.kb0; kb < it.kb1; ++kb, ++n) {
                     if (n < (uint32_t)pre) continue;                 // already requested above
                     const int s = n % STAGES;
@@ -155,7 +165,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
             SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
             uint32_t n = 0, seg = 0;
             bool ok = true;
+            if (grouped) pdl_wait();
             while (ok && it.next()) {
+                if (grouped && lane_group[it.tile % n_lane_tiles] < 0) continue;
                 const uint32_t acc = seg & 1, use = seg >> 1;
                 if (use > 0 && !mbar_wait(tempty_bar(acc), (use - 1) & 1, abort_flag)) break;   // epilogue has drained it
                 tc_fence_after();
@@ -187,6 +199,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
         SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
         uint32_t seg = 0, chunk_no = 0;
         while (it.next()) {
+            if (grouped && lane_group[it.tile % n_lane_tiles] < 0) continue;
             const uint32_t acc = seg & 1, use = seg >> 1;
             if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) break;
             tc_fence_after();
@@ -279,7 +292,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
 // ------------------------------------------------------------------- host side
 template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
 int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& to, void* out,
-              int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t stream) {
+              int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t stream,
+              const int* lane_group = nullptr, int group_rows = 0) {
     using Cfg = TileCfg<BN, TMA_OUT, SWAP>;
     auto kern = gemm_tc_kernel<BN, SWAP, EPI, TC, TMA_OUT>;
     static bool configured = false;
@@ -304,7 +318,7 @@ int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& t
     if (ctas <= 0) return TFF_ERR_LAUNCH;
     if (ctas > units) ctas = units;
     return tff_launch_pdl(kern, dim3((unsigned)ctas), dim3(NUM_THREADS), (size_t)Cfg::kSmemBytes, stream, tl, tc, to,
-                          (TC*)out, rows_lane, rows_col, K, ldo, stream_k, tff_device_error_flag());
+                          (TC*)out, rows_lane, rows_col, K, ldo, stream_k, tff_device_error_flag(), lane_group, group_rows);
 }
 
 template <int BN, bool SWAP, bool TMA_OUT>
@@ -412,4 +426,42 @@ TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, i
 TFF_API int tff_gemm_tc_gated(const void* A, const void* W, void* out, int M, int I, int K, int bn, int act,
                               cudaStream_t stream) {
     return gemm_tc_gated(A, W, out, M, I, K, bn, act, stream);
+}
+
+// Grouped products on the same kernel: the rows of A ([rows, K], rows a multiple of 128) are tiles of 128 rows that
+// each belong to one group (lane_group[tile] on the device; -1: the tile is not used), W is [groups * group_rows, K],
+// and tile t is multiplied with its group's rows of W:  out[rows, group_rows] = A W_g^T, or, gated, out[rows,
+// group_rows / 2] = act(A Wg_g^T) * (A Wu_g^T) with every group's gate and up rows alternating in blocks of 64 as
+// above.  The rows of a routed feed-forward's tokens, sorted by expert with every expert's share padded to 128.
+TFF_API int tff_gemm_tc_grouped(const void* A, const void* W, void* out, int out_is_bf16, int rows, int groups,
+                                int group_rows, int K, int bn, int gated, int act, const int* lane_group,
+                                cudaStream_t stream) {
+    if (rows <= 0 || groups <= 0 || group_rows <= 0) return TFF_OK;
+    if (K <= 0 || !lane_group || (act != 0 && act != 1)) return TFF_ERR_BAD_ARGUMENT;
+    if (K % 8 != 0 || rows % BM != 0 || (bn != 128 && bn != 256)) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
+    if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
+    CUtensorMap tl, tc, to;
+    if (!tff_tensor_map_2d(A, rows, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(W, (long long)groups * group_rows, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
+    if (gated) {
+        const int I = group_rows / 2;
+        if (group_rows % 128 != 0 || !out_is_bf16) return TFF_ERR_UNSUPPORTED;
+        if (!tff_tensor_map_2d(out, rows, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
+        if (act) {
+            if (bn == 256) return launch_tc<256, false, EPI_GEGLU, bf16, true>(tl, tc, to, out, rows, group_rows, K, I, 0, stream, lane_group, group_rows);
+            return launch_tc<128, false, EPI_GEGLU, bf16, true>(tl, tc, to, out, rows, group_rows, K, I, 0, stream, lane_group, group_rows);
+        }
+        if (bn == 256) return launch_tc<256, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, rows, group_rows, K, I, 0, stream, lane_group, group_rows);
+        return launch_tc<128, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, rows, group_rows, K, I, 0, stream, lane_group, group_rows);
+    }
+    const int elt = out_is_bf16 ? 2 : 4;
+    if (((long long)group_rows * elt) % 16 != 0) return TFF_ERR_UNSUPPORTED;
+    if (!tff_tensor_map_2d(out, rows, group_rows, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
+    if (out_is_bf16) {
+        if (bn == 256) return launch_tc<256, false, EPI_STORE, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
+        return launch_tc<128, false, EPI_STORE, bf16, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
+    }
+    if (bn == 256) return launch_tc<256, false, EPI_STORE, float, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
+    return launch_tc<128, false, EPI_STORE, float, true>(tl, tc, to, out, rows, group_rows, K, group_rows, 0, stream, lane_group, group_rows);
 }

@@ -61,18 +61,28 @@ moe_route_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, int 
         for (int k = 0; k < top; ++k) pair_weight[(size_t)t * top + k] /= total;
 }
 
+// pad_rows > 0: every expert's rows start at a multiple of pad_rows (= tile_rows): the sorted order then consists of
+// whole tiles of one expert each, and lane_group[row / pad_rows] names it (-1: a tile nobody uses), which is what the
+// grouped tcgen05 product reads.
 __global__ void moe_plan_kernel(int* __restrict__ counts, int E, int tile_rows, int* __restrict__ cursor,
                                 int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ tile_row_end,
-                                int* __restrict__ num_tiles) {
+                                int* __restrict__ num_tiles, int pad_rows, int* __restrict__ lane_group, int lane_tiles) {
     pdl_launch_dependents();
     pdl_wait();
+    if (lane_group)
+        for (int i = threadIdx.x; i < lane_tiles; i += blockDim.x) lane_group[i] = -1;
+    __syncthreads();
     if (threadIdx.x != 0) return;
     int off = 0, n = 0;
     for (int e = 0; e < E; ++e) {
         const int c = counts[e];
         counts[e] = 0;
+        if (pad_rows > 0) off = (off + pad_rows - 1) / pad_rows * pad_rows;
         cursor[e] = off;
-        for (int r = off; r < off + c; r += tile_rows) { tile_group[n] = e; tile_row0[n] = r; tile_row_end[n] = off + c; ++n; }
+        for (int r = off; r < off + c; r += tile_rows) {
+            tile_group[n] = e; tile_row0[n] = r; tile_row_end[n] = off + c; ++n;
+            if (lane_group) lane_group[r / pad_rows] = e;
+        }
         off += c;
     }
     *num_tiles = n;
@@ -82,7 +92,7 @@ template <typename TH>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restrict__ pair_expert,
                   const float* __restrict__ pair_weight, int weight_on_input, int* __restrict__ cursor,
-                  int* __restrict__ row_map, TH* __restrict__ x) {
+                  int* __restrict__ row_map, int* __restrict__ place_of_pair, TH* __restrict__ x) {
     __shared__ int place_s;
     pdl_launch_dependents();
     pdl_wait();
@@ -90,6 +100,7 @@ moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restric
     if (threadIdx.x == 0) {
         place_s = atomicAdd(&cursor[pair_expert[pair]], 1);
         row_map[place_s] = pair;
+        if (place_of_pair) place_of_pair[pair] = place_s;
     }
     __syncthreads();
     const int place = place_s;
@@ -101,7 +112,8 @@ moe_gather_kernel(const TH* __restrict__ h, int W, int top, const int* __restric
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __restrict__ pair_weight,
-                   int weight_on_output, float* __restrict__ residual, float* __restrict__ out) {
+                   int weight_on_output, const int* __restrict__ place_of_pair, float* __restrict__ residual,
+                   float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -110,7 +122,8 @@ moe_combine_kernel(const float* __restrict__ y, int W, int top, const float* __r
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
         const float w = weight_on_output ? pair_weight[(size_t)t * top + k] : 1.f;
-        acc = fmaf(w, y[((size_t)t * top + k) * W + i], acc);
+        const size_t pair = (size_t)t * top + k;              // y in (token, rank) order, or in the sorted order
+        acc = fmaf(w, y[(place_of_pair ? (size_t)place_of_pair[pair] : pair) * W + i], acc);
     }
     const size_t at = (size_t)t * W + i;
     out[at] = residual ? residual[at] + acc : acc;
@@ -140,27 +153,29 @@ TFF_API int tff_moe_route(const void* h, int h_dt, const void* w_router, int w_d
 }
 
 TFF_API int tff_moe_plan(int* counts, int E, int tile_rows, int* cursor, int* tile_group, int* tile_row0,
-                         int* tile_row_end, int* num_tiles, cudaStream_t stream) {
-    if (E <= 0 || tile_rows <= 0) return TFF_ERR_BAD_ARGUMENT;
-    return tff_launch_pdl(moe_plan_kernel, dim3(1), dim3(32), 0, stream, counts, E, tile_rows, cursor, tile_group,
-                          tile_row0, tile_row_end, num_tiles);
+                         int* tile_row_end, int* num_tiles, int pad_rows, int* lane_group, int lane_tiles,
+                         cudaStream_t stream) {
+    if (E <= 0 || tile_rows <= 0 || pad_rows < 0 || (pad_rows > 0 && pad_rows != tile_rows) || (lane_group && pad_rows <= 0))
+        return TFF_ERR_BAD_ARGUMENT;
+    return tff_launch_pdl(moe_plan_kernel, dim3(1), dim3(128), 0, stream, counts, E, tile_rows, cursor, tile_group,
+                          tile_row0, tile_row_end, num_tiles, pad_rows, lane_group, lane_tiles);
 }
 
 TFF_API int tff_moe_gather(const void* h, int h_dt, int pairs, int W, int top, const int* pair_expert,
-                           const float* pair_weight, int weight_on_input, int* cursor, int* row_map, void* x,
-                           cudaStream_t stream) {
+                           const float* pair_weight, int weight_on_input, int* cursor, int* row_map,
+                           int* place_of_pair, void* x, cudaStream_t stream) {
     if (pairs <= 0) return TFF_OK;
     if (h_dt == 0)
         return tff_launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (const float*)h, W, top,
-                              pair_expert, pair_weight, weight_on_input, cursor, row_map, (float*)x);
+                              pair_expert, pair_weight, weight_on_input, cursor, row_map, place_of_pair, (float*)x);
     return tff_launch_pdl(moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (const bf16*)h, W, top,
-                          pair_expert, pair_weight, weight_on_input, cursor, row_map, (bf16*)x);
+                          pair_expert, pair_weight, weight_on_input, cursor, row_map, place_of_pair, (bf16*)x);
 }
 
 TFF_API int tff_moe_combine(const float* y, int T, int W, int top, const float* pair_weight, int weight_on_output,
-                            float* residual, float* out, cudaStream_t stream) {
+                            const int* place_of_pair, float* residual, float* out, cudaStream_t stream) {
     if (T <= 0) return TFF_OK;
     dim3 grid(T, (W + 255) / 256);
     return tff_launch_pdl(moe_combine_kernel, grid, dim3(256), 0, stream, y, W, top, pair_weight, weight_on_output,
-                          residual, out);
+                          place_of_pair, residual, out);
 }

@@ -709,7 +709,7 @@ class CudaKernels:
                      ldc: int, c_gs: int, gated: str = "", activation: str = "silu", tiles=None, row_map=None) -> None:
         """c_g = a_g @ b_g^T ([M, K] x [N, K]^T) for ``groups`` groups whose operands lie a_gs, b_gs, c_gs elements apart
         (rows lda, ldb, ldc elements apart), float32 accumulation with a fixed order of additions.  ``gated``: b_g holds
-        2N rows, gate and up, "blocked" ([N gate | N up]) or "interleaved" (in eights: stack_gate_up), and
+        2N rows, gate and up, "blocked" ([N gate | N up]) or "interleaved" (alternating in blocks of 64: stack_gate_up), and
         c_g = act(a gate^T) * (a up^T).  ``tiles`` = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, tile rows)
         is the ragged form (rows of ``a`` sorted by group, the table on the device); ``row_map`` sends product row r to
         row row_map[r] of ``c``.  bfloat16 operands of aligned sizes run on the tensor cores (csrc/gemm_grouped_mma.cu),
@@ -733,12 +733,12 @@ class CudaKernels:
         assert tile_rows in (0, self.grouped_tile_rows(False)), "the tile table was planned for the other kernel"
         b2 = _vp(0)
         if gated:
-            b2 = _vp(b.data_ptr() + (8 if gated == "interleaved" else N) * ldb * b.element_size())
+            b2 = _vp(b.data_ptr() + (self.GATE_UP_BLOCK if gated == "interleaved" else N) * ldb * b.element_size())
         self._check(self.lib.tff_gemm_grouped(
             _ptr(a), _c_int(_dt(a)), ll(lda), ll(a_gs), _ptr(b), b2, _c_int(_dt(b)), ll(ldb), ll(b_gs),
             _ptr(c), _c_int(_dt(c)), ll(ldc), ll(c_gs), _ptr(tg), _ptr(tr0), _ptr(tre), _ptr(nt), _c_int(max_tiles),
             _ptr(row_map), _c_int(groups), _c_int(M), _c_int(N), _c_int(K), act,
-            _c_int(1 if gated == "interleaved" else 0), self._stream()), "gemm_grouped")
+            _c_int(self.GATE_UP_BLOCK if gated == "interleaved" else 0), self._stream()), "gemm_grouped")
         self.launches += 1
 
     GROUPED_MMA = os.environ.get("TFFINFER_GROUPED_MMA", "1") != "0"
@@ -747,20 +747,24 @@ class CudaKernels:
         """Whether a grouped product of these operands runs on the tensor-core kernel."""
         return (self.GROUPED_MMA and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
                 and all(v % 8 == 0 for v in (K, lda, a_gs, ldb, b_gs)) and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
-                and (not gated or (gated == "interleaved" and N % 8 == 0)))
+                and (not gated or (gated == "interleaved" and N % self.GATE_UP_BLOCK == 0)))
 
     def grouped_tile_rows(self, tensor_cores: bool) -> int:
         return int(self.lib.tff_gemm_grouped_mma_tile_rows() if tensor_cores else self.lib.tff_gemm_grouped_tile_rows())
 
-    @staticmethod
-    def stack_gate_up(gates, ups):
+    GATE_UP_BLOCK = 64       # rows of a block of the "interleaved" gate/up layout (gate_up_block above: the same)
+
+    @classmethod
+    def stack_gate_up(cls, gates, ups):
         """One tensor [E, 2*ff, W] from the experts' gate and up matrices, and the name of its layout: "interleaved"
-        (rows in eights: eight gate rows, the eight up rows of the same outputs, ...; what the tensor-core kernel's
-        epilogue wants) when ff is a multiple of 8, else "blocked" (all gate rows, then all up rows)."""
+        (64 gate rows, the 64 up rows of the same outputs, ...: what the tensor-core kernels' epilogues want, as
+        merge_gate_up lays out a dense feed-forward) when ff is a multiple of 64, else "blocked" (all gate rows, then
+        all up rows)."""
         g, u = torch.stack(list(gates), dim=0), torch.stack(list(ups), dim=0)
         E, ff, W = g.shape
-        if ff % 8 == 0:
-            w = torch.stack([g.view(E, ff // 8, 8, W), u.view(E, ff // 8, 8, W)], dim=2).reshape(E, 2 * ff, W)
+        b = cls.GATE_UP_BLOCK
+        if ff % b == 0:
+            w = torch.stack([g.view(E, ff // b, b, W), u.view(E, ff // b, b, W)], dim=2).reshape(E, 2 * ff, W)
             return w.contiguous(), "interleaved"
         return torch.cat([g, u], dim=1).contiguous(), "blocked"
 
@@ -787,6 +791,18 @@ class CudaKernels:
         # both products run on the same kernel (one tile table): the tensor-core one if both can
         tc = (self.grouped_on_tensor_cores(h, w_gate_up, W, W, 0, W, 2 * ff * W, layout, ff)
               and self.grouped_on_tensor_cores(h, w_down, ff, ff, 0, ff, W * ff, "", W))
+        if tc and self.GROUPED_TCGEN05 and P >= self.GROUPED_TCGEN05_FROM and W % 4 == 0:
+            # Prompt-sized: the tcgen05 product in its grouped form.  Every expert's rows are padded to whole tiles of 128
+            # in the sorted order, both products write in that order, and the sum gathers a token's rows from it.
+            rows = -(-(P + E * 127) // 128) * 128
+            pair_weight, row_map, tiles, x, lane_group, place = self.moe_dispatch(
+                h, w_router, top, renormalize, weight_on == "input", 128, padded_rows=rows)
+            act = torch.empty((rows, ff), dtype=h.dtype, device=h.device)
+            self.gemm_tc_grouped(x, w_gate_up, act, E, 2 * ff, W, lane_group, gated=True, activation=activation)
+            y = torch.empty((rows, W), dtype=torch.float32, device=h.device)
+            self.gemm_tc_grouped(act, w_down, y, E, W, ff, lane_group)
+            self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target, place)
+            return
         pair_weight, row_map, tiles, x = self.moe_dispatch(h, w_router, top, renormalize, weight_on == "input",
                                                            self.grouped_tile_rows(tc))
         act = torch.empty((P, ff), dtype=h.dtype, device=h.device)
@@ -796,10 +812,34 @@ class CudaKernels:
         self.gemm_grouped(act, w_down, y, E, 0, W, ff, ff, 0, ff, W * ff, W, 0, tiles=tiles, row_map=row_map)
         self.moe_combine(y, pair_weight if weight_on == "output" else None, top, residual, target)
 
-    def moe_dispatch(self, h, w_router, top: int, renormalize: bool, scale_rows: bool, tile_rows: int = 0):
+    GROUPED_TCGEN05 = os.environ.get("TFFINFER_GROUPED_TCGEN05", "1") != "0"
+    GROUPED_TCGEN05_FROM = 1024      # (token, expert) pairs of a step from which the experts run on the tcgen05 product
+
+    def gemm_tc_grouped(self, a, w, out, groups: int, group_rows: int, K: int, lane_group, gated: bool = False,
+                        activation: str = "silu") -> None:
+        """out = a @ w_g^T tile by tile of 128 rows of ``a``, tile t with group lane_group[t] (int32 on the device, -1: no
+        such tile) of ``w`` [groups, group_rows, K]; gated: w_g holds gate and up rows alternating in blocks of 64 and
+        out has group_rows / 2 columns.  The tcgen05 product of csrc/gemm_tc.cu in its grouped form."""
+        self._need_cuda(a, w, out, lane_group)
+        rows = a.shape[0]
+        assert a.dtype == w.dtype == torch.bfloat16 and a.shape[1] == K and rows % 128 == 0 and lane_group.numel() >= rows // 128
+        assert tuple(w.shape) == (groups, group_rows, K) and out.shape[0] == rows
+        assert out.shape[1] == (group_rows // 2 if gated else group_rows)
+        bn = 256 if (group_rows % 256 == 0 and rows >= 2048) else 128
+        self._check(self.lib.tff_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(rows), _c_int(groups),
+                                                 _c_int(group_rows), _c_int(K), _c_int(bn), _c_int(1 if gated else 0),
+                                                 _c_int(self.ACTIVATION_CODES[activation]), _ptr(lane_group),
+                                                 self._stream()), "gemm_tc_grouped")
+        self.launches += 1
+
+    def moe_dispatch(self, h, w_router, top: int, renormalize: bool, scale_rows: bool, tile_rows: int = 0,
+                     padded_rows: int = 0):
         """Router, choice and sorting of a routed feed-forward (csrc/moe.cu: route, plan, gather).  Returns
         (pair_weight float32 [T*top], row_map int32 [T*top]: sorted place -> pair, the tile table of the grouped
-        products, x [T*top, W]: the tokens' rows sorted by expert, times their weight when ``scale_rows``)."""
+        products, x [T*top, W]: the tokens' rows sorted by expert, times their weight when ``scale_rows``).  With
+        ``padded_rows`` (a multiple of ``tile_rows``, at least T*top + E*(tile_rows-1)) every expert's rows start at a
+        multiple of ``tile_rows``, x has that many rows, and two more are returned: lane_group (int32, the expert of
+        every tile of x, -1 for tiles nobody uses) and place_of_pair (int32 [T*top])."""
         T, W = h.shape
         E = w_router.shape[0]
         dev, P = h.device, T * top
@@ -809,30 +849,39 @@ class CudaKernels:
             self._moe_counts[(E, str(dev))] = counts
         bm = tile_rows or self.grouped_tile_rows(False)      # rows of a tile of the grouped product that follows
         max_tiles = -(-P // bm) + E
-        ints = torch.empty(2 * P + E + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
-        pair_expert, row_map, cursor = ints[:P], ints[P:2 * P], ints[2 * P:2 * P + E]
-        o = 2 * P + E
+        R = max(P, padded_rows)                              # rows of the sorted order
+        lane_tiles = padded_rows // bm if padded_rows else 0
+        ints = torch.empty(P + R + E + 3 * max_tiles + 1 + lane_tiles + (P if padded_rows else 0), dtype=torch.int32, device=dev)
+        pair_expert, row_map, cursor = ints[:P], ints[P:P + R], ints[P + R:P + R + E]
+        o = P + R + E
         tile_group, tile_row0, tile_row_end = ints[o:o + max_tiles], ints[o + max_tiles:o + 2 * max_tiles], ints[o + 2 * max_tiles:o + 3 * max_tiles]
-        num_tiles = ints[o + 3 * max_tiles:]
+        num_tiles = ints[o + 3 * max_tiles:o + 3 * max_tiles + 1]
+        lane_group = ints[o + 3 * max_tiles + 1:o + 3 * max_tiles + 1 + lane_tiles] if padded_rows else None
+        place = ints[o + 3 * max_tiles + 1 + lane_tiles:] if padded_rows else None
         pair_weight = torch.empty(P, dtype=torch.float32, device=dev)
         self._check(self.lib.tff_moe_route(_ptr(h), _c_int(_dt(h)), _ptr(w_router), _c_int(_dt(w_router)), _c_int(T), _c_int(W),
                                            _c_int(E), _c_int(top), _c_int(1 if renormalize else 0), _ptr(pair_expert),
                                            _ptr(pair_weight), _ptr(counts), self._stream()), "moe_route")
         self._check(self.lib.tff_moe_plan(_ptr(counts), _c_int(E), _c_int(bm), _ptr(cursor), _ptr(tile_group), _ptr(tile_row0),
-                                          _ptr(tile_row_end), _ptr(num_tiles), self._stream()), "moe_plan")
-        x = torch.empty((P, W), dtype=h.dtype, device=dev)
+                                          _ptr(tile_row_end), _ptr(num_tiles), _c_int(bm if padded_rows else 0),
+                                          _ptr(lane_group), _c_int(lane_tiles), self._stream()), "moe_plan")
+        x = torch.empty((R, W), dtype=h.dtype, device=dev)
         self._check(self.lib.tff_moe_gather(_ptr(h), _c_int(_dt(h)), _c_int(P), _c_int(W), _c_int(top), _ptr(pair_expert),
                                             _ptr(pair_weight), _c_int(1 if scale_rows else 0), _ptr(cursor),
-                                            _ptr(row_map), _ptr(x), self._stream()), "moe_gather")
+                                            _ptr(row_map), _ptr(place), _ptr(x), self._stream()), "moe_gather")
         self.launches += 3
-        return pair_weight, row_map, (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, bm), x
+        tiles = (tile_group, tile_row0, tile_row_end, num_tiles, max_tiles, bm)
+        if padded_rows:
+            return pair_weight, row_map, tiles, x, lane_group, place
+        return pair_weight, row_map, tiles, x
 
-    def moe_combine(self, y, pair_weight, top: int, residual, out) -> None:
-        """out[t] = residual[t] + sum_k w[t, k] * y[t*top + k] in the order of k (pair_weight None: plain sum)."""
+    def moe_combine(self, y, pair_weight, top: int, residual, out, place_of_pair=None) -> None:
+        """out[t] = residual[t] + sum_k w[t, k] * y[t*top + k] in the order of k (pair_weight None: plain sum); with
+        ``place_of_pair`` the row of pair t*top + k is y[place_of_pair[t*top + k]] (y in the sorted order)."""
         T, W = out.shape
         self._check(self.lib.tff_moe_combine(_ptr(y), _c_int(T), _c_int(W), _c_int(top), _ptr(pair_weight),
-                                             _c_int(1 if pair_weight is not None else 0), _ptr(residual), _ptr(out),
-                                             self._stream()), "moe_combine")
+                                             _c_int(1 if pair_weight is not None else 0), _ptr(place_of_pair),
+                                             _ptr(residual), _ptr(out), self._stream()), "moe_combine")
         self.launches += 1
 
     # ------------------------------------------------------- gated recurrence over a state of one vector
