@@ -281,16 +281,19 @@ def test_routed_experts(ops, dtype, E, top, ff, W, T):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_latent_attention_far_keys_and_borrowed_cache(ops, dtype):
+@pytest.mark.parametrize("dim,rot,rdims,vd", [(24, 12, 8, 20), (24, 8, 4, 16)])
+def test_latent_attention_far_keys_and_borrowed_cache(ops, dtype, dim, rot, rdims, vd):
     """A latent attention layer alone: 700 tokens in portions that end inside pages, then single tokens, with sharp
     queries (a missed key among hundreds shows), part of the rotated part left unrotated; then a second layer with its
-    own queries and up-projections reading the first one's cached vectors."""
+    own queries and up-projections reading the first one's cached vectors.  At the end the whole prompt as one step that
+    starts at position 0: with sizes that are multiples of 8, in bfloat16, that is the form with per-head keys, the
+    second layer taking the step's latents from the first."""
     from tffinfer_b200.parts.latent import LatentAttention
     from tffinfer_b200.parts.position import ScaledRotary
     from tffinfer_b200.parts.base import LayerContext
     dev, dt = "cuda", getattr(torch, dtype)
     g = torch.Generator().manual_seed(4)
-    W, H, dim, rot, rdims, vd, qr, kr, page, eps = 64, 3, 24, 12, 8, 20, 16, 40, 16, 1e-5
+    W, H, qr, kr, page, eps = 64, 3, 16, 40, 16, 1e-5
     T = 700
     h = torch.randn(T, W, generator=g).to(dt)
     names = {"dq": (qr, W), "dq.norm": (qr,), "uq": (H * (dim + rot), qr), "dkv": (kr + rot, W), "dkv.norm": (kr,),
@@ -334,6 +337,20 @@ def test_latent_attention_far_keys_and_borrowed_cache(ops, dtype):
     for i in range(2):
         err = float((torch.cat(got[i]) - want[i]).abs().max() / want[i].abs().max())
         assert err < (3e-5 if dtype == "float32" else 3e-2), f"layer {i} off by {err:.3g}"
+    import numpy as np
+    cache.fill_(float("nan"))
+    batch = fake_batch([T], [0], dev, page)
+    batch.h_pos_start = np.array([0])
+    table = torch.arange(T // page + 1, dtype=torch.int32, device=dev).reshape(1, -1)
+    shared = {}
+    for i, m in enumerate(layers):
+        ctx = LayerContext(batch=batch, ops=ops, kv_cache=cache, kv_layer=0, block_table=table, page_size=page,
+                           write_cache=(i == 0), position=pos, shared=shared)
+        whole = m.forward(h.to(dev).contiguous(), ctx, None).double().cpu().clone()
+        ops.reset_accumulators()
+        err = float((whole - want[i]).abs().max() / want[i].abs().max())
+        assert err < (3e-5 if dtype == "float32" else 3e-2), f"whole prompt, layer {i} off by {err:.3g}"
+    assert (dtype == "bfloat16" and (dim + rot) % 8 == 0) == bool(shared), "which form ran is not the one expected"
 
 
 def test_norm_with_a_weight_around_zero(ops):

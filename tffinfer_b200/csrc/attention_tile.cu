@@ -32,6 +32,9 @@ struct TileArgs {
     const float* temp; const float* r1; const float* r2;
     float out_scale; int q_ld, out_ld, out_off;
     int splits; float* part_o; float* part_ml;     // splits > 1: shares of the key range, merged by a second kernel
+    // Keys and values of THIS step's tokens in plain rows instead of the cache (tensor-core form only; every request of the
+    // step must start at position 0): key n of a request is row q_start + n, head h at columns h*d (values: h*dv).
+    const void* k_dense; const void* v_dense; int k_ld, v_ld;
 };
 
 template <typename TQ, typename TC, int NC>
@@ -308,7 +311,8 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr int MROWS = 16 * RG, MTHREADS = 128 * RG;
     const int d = a.d, dv = a.dv, G = a.nq / a.nkv;
-    const bool own_v = a.v_offset != 0;
+    const bool dense = a.k_dense != nullptr;
+    const bool own_v = a.v_offset != 0 || dense;
     const int kst = gm.kst, vst = gm.vst, dpad = gm.dpad;
     bf16* Qs = (bf16*)smraw;                                    // [MROWS][kst]
     bf16* Ks = Qs + MROWS * kst;                                // [MKB][kst]
@@ -320,6 +324,7 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
     int* row_p = (int*)(m_fin + MROWS);
     int* row_lo = row_p + MROWS;
     const bf16** key_src = (const bf16**)(row_lo + MROWS);     // [MKB] (8-byte aligned: an even number of 4-byte words lies ahead)
+    const bf16** val_src = key_src + MKB;                      // [MKB]
 
     pdl_launch_dependents();
     const int b = blockIdx.z, kvh = blockIdx.y;
@@ -380,12 +385,21 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
         if (tid < MKB) {
             const int n = k0 + tid;
             const bf16* src = nullptr;
+            const bf16* vsrc = nullptr;
             if (n >= lo_min && n <= p_max) {
-                const int page = table[n / a.page_size];
-                if (page >= 0)
-                    src = cache + (size_t)page * a.page_stride + (size_t)kvh * a.head_stride + (size_t)(n % a.page_size) * a.slot;
+                if (dense) {
+                    src = (const bf16*)a.k_dense + (size_t)(t0 + n - pos0) * a.k_ld + (size_t)kvh * d;
+                    vsrc = (const bf16*)a.v_dense + (size_t)(t0 + n - pos0) * a.v_ld + (size_t)kvh * dv;
+                } else {
+                    const int page = table[n / a.page_size];
+                    if (page >= 0) {
+                        src = cache + (size_t)page * a.page_stride + (size_t)kvh * a.head_stride + (size_t)(n % a.page_size) * a.slot;
+                        vsrc = src + a.v_offset;
+                    }
+                }
             }
             key_src[tid] = src;
+            val_src[tid] = vsrc;
         }
         __syncthreads();
         // asynchronous 16-byte copies straight into shared memory (zero fill where there is no key or the row has
@@ -394,13 +408,13 @@ attention_tile_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ c
             const int kk = idx / dch, c = idx % dch;
             const bf16* src = key_src[kk];
             const bool ok = src && c * 8 < d;
-            cp_async_16(sm_addr(Ks + kk * kst + c * 8), ok ? (const void*)(src + c * 8) : (const void*)cache, ok ? 16 : 0);
+            cp_async_16(sm_addr(Ks + kk * kst + c * 8), ok ? (const void*)(src + c * 8) : (const void*)q, ok ? 16 : 0);
         }
         for (int idx = tid; idx < MKB * vch; idx += MTHREADS) {
             const int kk = idx / vch, c = idx % vch;
-            const bf16* src = key_src[kk];
+            const bf16* src = val_src[kk];
             const bool ok = src && c * 8 < dv;
-            cp_async_16(sm_addr(Vs + kk * vst + c * 8), ok ? (const void*)(src + a.v_offset + c * 8) : (const void*)cache, ok ? 16 : 0);
+            cp_async_16(sm_addr(Vs + kk * vst + c * 8), ok ? (const void*)(src + c * 8) : (const void*)q, ok ? 16 : 0);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -514,9 +528,12 @@ static bool tile_mma_enabled() {
 int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs& a, int num_requests, int max_q_len,
                     int num_tokens, cudaStream_t stream) {
     const int G = a.nq / a.nkv;
-    const bool own_v = a.v_offset != 0;
-    if (!tile_mma_enabled() || (a.d & 7) || (a.slot & 7) || (a.q_ld & 7) || (a.page_stride & 7) || (a.v_offset & 7) ||
-        ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || (own_v && (a.dv & 7)) || a.dv > 512)
+    const bool dense = a.k_dense != nullptr;
+    const bool own_v = a.v_offset != 0 || dense;
+    if (!tile_mma_enabled() || (a.d & 7) || (a.q_ld & 7) || ((uintptr_t)q & 15) || (own_v && (a.dv & 7)) || a.dv > 512)
+        return TFF_ERR_UNSUPPORTED;
+    if (dense ? ((a.k_ld & 7) || (a.v_ld & 7) || ((uintptr_t)a.k_dense & 15) || ((uintptr_t)a.v_dense & 15))
+              : ((a.slot & 7) || (a.page_stride & 7) || (a.v_offset & 7) || ((uintptr_t)cache & 15)))
         return TFF_ERR_UNSUPPORTED;
     if (num_requests > 65535 || a.nkv > 65535) return TFF_ERR_UNSUPPORTED;
     int nt = 2;
@@ -529,7 +546,7 @@ int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs&
     const int rg = rows_most <= 16 ? 1 : (rows_most <= 32 ? 2 : 4);
     const int MROWS = 16 * rg;
     const size_t smem = 2 * ((size_t)(MROWS + MKB) * gm.kst + (own_v ? (size_t)MKB * gm.vst : 0) + (size_t)MROWS * PST) +
-                        4 * ((size_t)MROWS * SST + 2 * MROWS) + 4 * 2 * MROWS + 8 * MKB;
+                        4 * ((size_t)MROWS * SST + 2 * MROWS) + 4 * 2 * MROWS + 2 * 8 * MKB;
     if (smem > 220 * 1024) return TFF_ERR_UNSUPPORTED;
     const int tiles = (rows_most + MROWS - 1) / MROWS;
     dim3 grid(tiles * a.splits, a.nkv, num_requests);
@@ -565,14 +582,19 @@ int launch_tile_mma(const void* q, const void* cache, void* out, const TileArgs&
 // layer's offset already added); ``planes`` 2: values in the second plane of a page, 1: the value is the first dv
 // elements of the key's slot.  is_bf16: q, out and the cache are bfloat16, else float32.  splits > 1: every tile's key
 // range in that many shares (float32 workspaces part_o [tokens*nq, splits, dv] and part_ml [tokens*nq, splits, 2]) and a
-// merge kernel; for steps of few rows behind long contexts, which would otherwise be a handful of CTAs.
+// merge kernel; for steps of few rows behind long contexts, which would otherwise be a handful of CTAs.  k_dense / v_dense
+// (bfloat16 [tokens, k_ld] / [tokens, v_ld], both or neither): the keys and values of this step's tokens in plain rows
+// instead of the cache, for steps whose requests all start at position 0.
 TFF_API int tff_attention_tile(
     const void* q, int is_bf16, int q_ld, const int* q_start, const int* pos_start, const int* block_table,
     int table_width, const void* cache, long long page_stride, int planes, int page_size, int slot,
     void* out, int out_ld, int out_off, int num_requests, int max_q_len, int nq, int nkv, int d, int dv, float scale,
     int window, int chunk, const float* temp, const float* r1, const float* r2, float out_scale,
-    int num_tokens, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+    int num_tokens, int splits, float* part_o, float* part_ml,
+    const void* k_dense, const void* v_dense, int k_ld, int v_ld, cudaStream_t stream) {
     if (num_requests <= 0 || max_q_len <= 0) return TFF_OK;
+    if ((k_dense == nullptr) != (v_dense == nullptr)) return TFF_ERR_BAD_ARGUMENT;
+    if (k_dense) { planes = 2; slot = d > dv ? d : dv; page_size = 1; }      // no cache is read: any consistent geometry
     if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || dv <= 0 || slot < d || page_size <= 0 || window < 0 || chunk < 0 ||
         (planes != 1 && planes != 2) || (planes == 2 && slot < dv) || (planes == 1 && dv > d) || ((r1 == nullptr) != (r2 == nullptr)))
         return TFF_ERR_BAD_ARGUMENT;
@@ -585,6 +607,11 @@ TFF_API int tff_attention_tile(
     a.q_ld = q_ld; a.out_ld = out_ld; a.out_off = out_off;
     if (splits < 1 || (splits > 1 && (!part_o || !part_ml))) return TFF_ERR_BAD_ARGUMENT;
     a.splits = splits; a.part_o = part_o; a.part_ml = part_ml;
+    a.k_dense = k_dense; a.v_dense = v_dense; a.k_ld = k_ld; a.v_ld = v_ld;
+    if (k_dense) {                                   // the tensor-core form or nothing
+        if (!is_bf16) return TFF_ERR_UNSUPPORTED;
+        return launch_tile_mma(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
+    }
     if (is_bf16) {
         const int st = launch_tile_mma(q, cache, out, a, num_requests, max_q_len, num_tokens, stream);
         if (st != TFF_ERR_UNSUPPORTED) return st;

@@ -22,7 +22,7 @@ latent_finish_kernel(float* __restrict__ proj, int ld, int clear_input, int q_ra
                      const float* __restrict__ wq, const float* __restrict__ wkv, float eps, const float* __restrict__ freq,
                      const int* __restrict__ positions, const int* __restrict__ tok_req,
                      const int* __restrict__ block_table, int table_width, TC* __restrict__ cache, long long page_stride,
-                     int page_size, int slot_elems, TQ* __restrict__ cq) {
+                     int page_size, int slot_elems, TQ* __restrict__ cq, TC* __restrict__ dense_out) {
     __shared__ float red[32];
     pdl_launch_dependents();
     const int t = blockIdx.x, tid = threadIdx.x;
@@ -44,6 +44,7 @@ latent_finish_kernel(float* __restrict__ proj, int ld, int clear_input, int q_ra
     const int page = block_table[(size_t)tok_req[t] * table_width + pos / page_size];
     if (page < 0) return;                                        // no page: the host never schedules this
     TC* slot = cache + (size_t)page * page_stride + (size_t)(pos % page_size) * slot_elems;
+    TC* drow = dense_out ? dense_out + (size_t)t * (kv_rank + rot_dim) : nullptr;   // the same vector in a plain row
     float* src = row + q_rank;
     float ss = 0.f;
     for (int i = tid; i < kv_rank; i += 128) { const float x = src[i]; ss = fmaf(x, x, ss); }
@@ -53,6 +54,7 @@ latent_finish_kernel(float* __restrict__ proj, int ld, int clear_input, int q_ra
         const float x = src[i];
         if (clear_input) src[i] = 0.f;
         slot[i] = from_f32<TC>((x * r) * wkv[i]);
+        if (drow) drow[i] = slot[i];
     }
     float* rs = src + kv_rank;
     TC* rd = slot + kv_rank;
@@ -64,18 +66,37 @@ latent_finish_kernel(float* __restrict__ proj, int ld, int clear_input, int q_ra
         sincosf((float)pos * freq[i], &s, &c);
         rd[2 * i] = from_f32<TC>(u * c - v * s);
         rd[2 * i + 1] = from_f32<TC>(v * c + u * s);
+        if (drow) { drow[kv_rank + 2 * i] = rd[2 * i]; drow[kv_rank + 2 * i + 1] = rd[2 * i + 1]; }
     }
     for (int i = 2 * half + tid; i < rot_dim; i += 128) {
         const float x = rs[i];
         if (clear_input) rs[i] = 0.f;
         rd[i] = from_f32<TC>(x);
+        if (drow) drow[kv_rank + i] = rd[i];
     }
+}
+
+// keys[t, h, dim .. dim + rot_dim) = latent[t, kv_rank .. kv_rank + rot_dim): the shared rotated key part into every head's
+// key row, for the form of the attention that makes per-head keys (one warp per (token, head))
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_spread_kernel(const T* __restrict__ latent, int kv_rank, int rot_dim, T* __restrict__ keys, int dim, int heads,
+                     int num_tokens) {
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)num_tokens * heads) return;
+    const int t = (int)(item / heads), h = (int)(item % heads);
+    pdl_wait();
+    const T* src = latent + (size_t)t * (kv_rank + rot_dim) + kv_rank;
+    T* dst = keys + ((size_t)t * heads + h) * (dim + rot_dim) + dim;
+    for (int i = lane; i < rot_dim; i += 32) dst[i] = src[i];
 }
 
 template <typename TQ>
 __global__ void __launch_bounds__(128)
-latent_q_rot_kernel(const TQ* __restrict__ q, int dim, int rot_dim, int rot_dims, const float* __restrict__ freq,
-                    const int* __restrict__ positions, TQ* __restrict__ q_lat, int kv_rank, int heads, int num_tokens) {
+latent_q_rot_kernel(const TQ* q, int dim, int rot_dim, int rot_dims, const float* __restrict__ freq,
+                    const int* __restrict__ positions, TQ* q_lat, int kv_rank, int heads, int num_tokens) {
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + warp;
@@ -104,7 +125,7 @@ TFF_API int tff_latent_finish(float* proj, int ld, int clear_input, int q_rank, 
                               const float* wq, const float* wkv, float eps, const float* freq, const int* positions,
                               const int* tok_req, const int* block_table, int table_width, void* cache,
                               long long page_stride, int page_size, int slot_elems, void* cq, int is_bf16,
-                              int num_tokens, cudaStream_t stream) {
+                              void* dense_out, int num_tokens, cudaStream_t stream) {
     if (num_tokens <= 0) return TFF_OK;
     if (!proj || q_rank < 0 || kv_rank < 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1))
         return TFF_ERR_BAD_ARGUMENT;
@@ -114,10 +135,10 @@ TFF_API int tff_latent_finish(float* proj, int ld, int clear_input, int q_rank, 
     if (is_bf16)
         return tff_launch_pdl(latent_finish_kernel<bf16, bf16>, dim3(num_tokens), dim3(128), 0, stream, proj, ld, clear_input,
                               q_rank, kv_rank, rot_dim, rot_dims, wq, wkv, eps, freq, positions, tok_req, block_table,
-                              table_width, (bf16*)cache, page_stride, page_size, slot_elems, (bf16*)cq);
+                              table_width, (bf16*)cache, page_stride, page_size, slot_elems, (bf16*)cq, (bf16*)dense_out);
     return tff_launch_pdl(latent_finish_kernel<float, float>, dim3(num_tokens), dim3(128), 0, stream, proj, ld, clear_input,
                           q_rank, kv_rank, rot_dim, rot_dims, wq, wkv, eps, freq, positions, tok_req, block_table,
-                          table_width, (float*)cache, page_stride, page_size, slot_elems, (float*)cq);
+                          table_width, (float*)cache, page_stride, page_size, slot_elems, (float*)cq, (float*)dense_out);
 }
 
 TFF_API int tff_latent_q_rot(const void* q, int dim, int rot_dim, int rot_dims, const float* freq, const int* positions,
@@ -131,4 +152,17 @@ TFF_API int tff_latent_q_rot(const void* q, int dim, int rot_dim, int rot_dims, 
                               (bf16*)q_lat, kv_rank, heads, num_tokens);
     return tff_launch_pdl(latent_q_rot_kernel<float>, grid, dim3(128), 0, stream, (const float*)q, dim, rot_dim, rot_dims, freq, positions,
                           (float*)q_lat, kv_rank, heads, num_tokens);
+}
+
+TFF_API int tff_latent_spread(const void* latent, int kv_rank, int rot_dim, void* keys, int dim, int heads, int is_bf16,
+                              int num_tokens, cudaStream_t stream) {
+    if (num_tokens <= 0 || rot_dim <= 0) return TFF_OK;
+    if (!latent || !keys || kv_rank < 0 || dim < 0 || heads <= 0) return TFF_ERR_BAD_ARGUMENT;
+    const long long items = (long long)num_tokens * heads;
+    dim3 grid((unsigned)((items + 3) / 4));
+    if (is_bf16)
+        return tff_launch_pdl(latent_spread_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)latent, kv_rank, rot_dim,
+                              (bf16*)keys, dim, heads, num_tokens);
+    return tff_launch_pdl(latent_spread_kernel<float>, grid, dim3(128), 0, stream, (const float*)latent, kv_rank, rot_dim,
+                          (float*)keys, dim, heads, num_tokens);
 }

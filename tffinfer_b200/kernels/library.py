@@ -662,20 +662,28 @@ class CudaKernels:
 
     def attention_tile(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, dv, scale,
                        window: int = 0, chunk: int = 0, temp=None, r1=None, r2=None, out_scale: float = 1.0,
-                       out_off: int = 0, num_splits=None) -> None:
+                       out_off: int = 0, num_splits=None, dense=None) -> None:
         """q [T, nq*d] against the paged cache -> columns out_off .. out_off + nq*dv of ``out`` (times out_scale), in
         float32 arithmetic whatever the storage type.  The cache has two planes (keys, values) or one (the value
         of a token is the first dv elements of its key).  Visibility: causal, within ``window`` keys, within the
         query's block of ``chunk`` positions.  Scores: (q . k) * scale * temp[h] - r1[h] * ln(1 + r2[h] * distance)
-        (temp, r1, r2 float32 [nq] or None)."""
+        (temp, r1, r2 float32 [nq] or None).  ``dense`` = (keys [T, nkv*d], values [T, nkv*dv]) of this step's own tokens
+        instead of the cache: for steps whose requests all start at position 0 (bfloat16, tensor-core form only)."""
         self._need_cuda(q, block_table, out, temp, r1, r2)
         T = q.shape[0]
-        planes, slot = kv_cache.shape[2], kv_cache.shape[-1]
-        assert kv_cache.dtype == q.dtype == out.dtype and q.shape[1] == nq * d
-        assert tuple(kv_cache.shape[3:5]) == (nkv, page_size) and out.shape[0] == T and out.shape[1] >= out_off + nq * dv
+        assert q.dtype == out.dtype and q.shape[1] == nq * d and out.shape[0] == T and out.shape[1] >= out_off + nq * dv
         for v in (temp, r1, r2):
             assert v is None or (v.dtype == torch.float32 and v.numel() == nq)
-        c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
+        kd = vd = None
+        if dense is not None:
+            kd, vd = dense
+            self._need_cuda(kd, vd)
+            assert kd.dtype == vd.dtype == q.dtype and tuple(kd.shape) == (T, nkv * d) and tuple(vd.shape) == (T, nkv * dv)
+            planes, slot, c_ptr, page_stride = 2, max(d, dv), _vp(0), 0
+        else:
+            planes, slot = kv_cache.shape[2], kv_cache.shape[-1]
+            assert kv_cache.dtype == q.dtype and tuple(kv_cache.shape[3:5]) == (nkv, page_size)
+            c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
         splits = self.tile_splits(batch, nq, nkv, window, chunk) if num_splits is None else int(num_splits)
         part_o = part_ml = None
         if splits > 1:
@@ -687,7 +695,8 @@ class CudaKernels:
             _c_int(slot), _ptr(out), _c_int(out.shape[1]), _c_int(out_off), _c_int(batch.num_requests),
             _c_int(batch.max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(dv), _c_float(scale), _c_int(window),
             _c_int(chunk), _ptr(temp), _ptr(r1), _ptr(r2), _c_float(out_scale), _c_int(T), _c_int(splits), _ptr(part_o),
-            _ptr(part_ml), self._stream()), "attention_tile")
+            _ptr(part_ml), _ptr(kd), _ptr(vd), _c_int(kd.shape[1] if kd is not None else 0),
+            _c_int(vd.shape[1] if vd is not None else 0), self._stream()), "attention_tile")
         self.launches += 2 if splits > 1 else 1
 
     def tile_splits(self, batch, nq: int, nkv: int, window: int = 0, chunk: int = 0) -> int:
@@ -919,21 +928,34 @@ class CudaKernels:
     GRU_CHUNKED_FROM = 32         # longest portion of a step from which the recurrence runs chunk by chunk
 
     # ------------------------------------------------------- latent attention
+    PER_HEAD_FROM = 128       # longest portion of a step of whole prompts from which a latent attention makes per-head keys
+
     def latent_attend(self, h, w_down, q_norm_w, kv_norm_w, eps: float, w_uq, w_uk_t, w_uv, freq, batch, block_table,
                       kv_cache, kv_layer, page_size, out, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int,
-                      kv_rank: int, scale: float, write_cache: bool) -> None:
+                      kv_rank: int, scale: float, write_cache: bool, w_uk=None, shared=None) -> None:
         """The whole of a latent attention between its input rows and its output projection -> out [T, heads*vdim].
         ``w_down`` rows [query latent (q_rank) | kv latent (kv_rank) | shared rotated key part (rot_dim)], the last two
         absent when the layer reads another layer's cache (``write_cache`` False).  The cache has one plane with a slot
         [c | r] of kv_rank + rot_dim elements per token.  Per-head keys W_uk c are never made: the query's unrotated
         part goes through W_uk^T instead (``w_uk_t`` [heads, kv_rank, dim]), attention then runs with one shared
         key/value head over the slots (keys the whole slot, values its first kv_rank elements), and W_uv [heads*vdim,
-        kv_rank] takes every head's mixed latent to its value size."""
+        kv_rank] takes every head's mixed latent to its value size.
+
+        A step of whole prompts (every request starts at position 0, bfloat16, aligned sizes) takes the other form: the
+        step's latents are also kept in plain rows (``shared``, a dict that lives for the step, hands them to the layers
+        that read this layer's cache), per-head keys [W_uk c | r] and values W_uv c of the step's tokens are made by
+        grouped products (``w_uk`` [heads*dim, kv_rank]), and attention runs with keys of dim + rot_dim and values of
+        vdim elements: a fifth of the absorbed form's arithmetic at the sizes of a large model.  The cache is written
+        either way."""
         if isinstance(h, DeferredNorm):
             h = h.materialize()
         T = h.shape[0]
         dev, dt = h.device, h.dtype
         slot = kv_rank + rot_dim
+        whole = (dt == torch.bfloat16 and shared is not None and getattr(batch, "h_pos_start", None) is not None
+                 and batch.max_q_len >= self.PER_HEAD_FROM and not np.any(batch.h_pos_start[:batch.num_requests])
+                 and slot % 8 == 0 and kv_rank % 8 == 0)
+        key = ("latent rows", kv_cache.data_ptr(), kv_layer)
         assert kv_cache is not None and kv_cache.shape[2] == 1 and kv_cache.shape[3] == 1 and kv_cache.shape[-1] == slot
         assert w_down.shape[0] >= (q_rank + slot if write_cache else q_rank)      # rows beyond are padding
         f, rot_dims, mag, inter = freq if freq is not None else (None, 0, 1.0, True)
@@ -942,10 +964,31 @@ class CudaKernels:
         proj = self.projection_buffer(T, w_down.shape[0], dev, dt)
         self.gemm(h, w_down, proj)
         cq = torch.empty((T, q_rank), dtype=dt, device=dev)
+        rows = None
+        if whole and write_cache:
+            rows = shared[key] = torch.empty((T, slot), dtype=dt, device=dev)
+        elif whole:
+            rows = shared.get(key)
         self.latent_finish(proj, cq, q_norm_w, kv_norm_w, eps, f, rot_dim, rot_dims, batch, block_table, kv_cache, kv_layer,
-                           page_size, q_rank, kv_rank if write_cache else 0)
+                           page_size, q_rank, kv_rank if write_cache else 0, dense_out=rows if write_cache else None)
         q = torch.empty((T, heads * (dim + rot_dim)), dtype=dt, device=dev)
         self.gemm(cq, w_uq, q)
+        if (rows is not None and w_uk is not None and (dim + rot_dim) % 8 == 0 and vdim % 8 == 0
+                and tuple(rows.shape) == (T, slot)):
+            self.latent_q_rot(q, q, f, batch, heads, dim, rot_dim, rot_dims, dim)          # in place: the head's own row
+            keys = torch.empty((T, heads * (dim + rot_dim)), dtype=dt, device=dev)
+            self.gemm_grouped(rows, w_uk, keys, heads, T, dim, kv_rank, slot, 0, kv_rank, dim * kv_rank,
+                              heads * (dim + rot_dim), dim + rot_dim)
+            self._check(self.lib.tff_latent_spread(_ptr(rows), _c_int(kv_rank), _c_int(rot_dim), _ptr(keys), _c_int(dim),
+                                                   _c_int(heads), _c_int(_dt(keys)), _c_int(T), self._stream()),
+                        "latent_spread")
+            self.launches += 1
+            values = torch.empty((T, heads * vdim), dtype=dt, device=dev)
+            self.gemm_grouped(rows, w_uv, values, heads, T, vdim, kv_rank, slot, 0, kv_rank, vdim * kv_rank,
+                              heads * vdim, vdim)
+            self.attention_tile(q, batch, block_table, kv_cache, kv_layer, page_size, out, heads, heads, dim + rot_dim,
+                                vdim, scale, dense=(keys, values))
+            return
         q_lat = torch.empty((T, heads * slot), dtype=dt, device=dev)
         self.gemm_grouped(q, w_uk_t, q_lat, heads, T, kv_rank, dim, heads * (dim + rot_dim), dim + rot_dim,
                           dim, kv_rank * dim, heads * slot, slot)
@@ -956,9 +999,10 @@ class CudaKernels:
                           heads * vdim, vdim)
 
     def latent_finish(self, proj, cq, q_norm_w, kv_norm_w, eps, freq, rot_dim, rot_dims, batch, block_table, kv_cache,
-                      kv_layer, page_size, q_rank, kv_rank) -> None:
+                      kv_layer, page_size, q_rank, kv_rank, dense_out=None) -> None:
         """csrc/latent.cu: the float32 rows [q latent | kv latent | rotated key part] -> normed query latents ``cq`` and,
-        with kv_rank > 0, the token's cache slot [normed kv latent | rotated key part]."""
+        with kv_rank > 0, the token's cache slot [normed kv latent | rotated key part] (and the same vector into row t of
+        ``dense_out`` [T, slot], when given)."""
         self._need_cuda(proj, cq, q_norm_w, kv_norm_w, freq, block_table)
         T = proj.shape[0]
         c_ptr, page_stride = self._layer_cache(kv_cache, kv_layer)
@@ -968,13 +1012,14 @@ class CudaKernels:
             _c_int(rot_dims), _ptr(q_norm_w), _ptr(kv_norm_w), _c_float(eps), _ptr(freq), _ptr(batch.positions),
             _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]), c_ptr if kv_rank > 0 else _vp(0),
             ctypes.c_longlong(page_stride), _c_int(page_size), _c_int(kv_cache.shape[-1]), _ptr(cq), _c_int(_dt(cq)),
-            _c_int(T), self._stream()), "latent_finish")
+            _ptr(dense_out), _c_int(T), self._stream()), "latent_finish")
         if clear:
             self._acc_zero[proj.data_ptr()] = True
         self.launches += 1
 
     def latent_q_rot(self, q, q_lat, freq, batch, heads, dim, rot_dim, rot_dims, kv_rank) -> None:
-        """The rotated part of every query head of the rows ``q`` into its place in ``q_lat`` (same type)."""
+        """The rotated part of every query head of the rows ``q`` into its place in ``q_lat`` (same type; a head's row
+        of ``q_lat`` has kv_rank + rot_dim elements, so with kv_rank = dim and q_lat = q the rotation is in place)."""
         assert q.dtype == q_lat.dtype
         self._check(self.lib.tff_latent_q_rot(_ptr(q), _c_int(dim), _c_int(rot_dim), _c_int(rot_dims), _ptr(freq),
                                               _ptr(batch.positions), _ptr(q_lat), _c_int(_dt(q_lat)), _c_int(kv_rank),

@@ -10,7 +10,8 @@ For a token with mixer input h at position p (all norms x * rsqrt(mean(x^2) + ep
 The rotation is the layer's position encoding (``frequencies()``: interleaved pairs).  The cache need is one plane
 with a slot of kv_rank + rot_dim elements per token, [c | r].  A layer built with ``shared_kv`` has no W_dkv and reads
 the slots another layer wrote (its schedule entry names that layer's entry in ``cache_of``); it has its own W_uk,
-W_uv and queries.  Per-head keys and values are never materialised (kernels/library.py ``latent_attend``)."""
+W_uv and queries.  Per-head keys and values of cached tokens are never materialised; a step of whole prompts makes
+those of its own tokens (kernels/library.py ``latent_attend``)."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -37,7 +38,7 @@ class LatentAttention(Mixer):
         self.names = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
                       "uv": "uv", "o": "o"}
         self.names.update(names or {})
-        self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.w_o = self.q_norm_w = self.kv_norm_w = None
+        self.w_down = self.w_uq = self.w_uk_t = self.w_uk = self.w_uv = self.w_o = self.q_norm_w = self.kv_norm_w = None
 
     def cache_need(self):
         return KVNeed(1, self.kv_rank + self.rot_dim, 0, planes=1)
@@ -67,6 +68,7 @@ class LatentAttention(Mixer):
         self.w_uq = tensors[n["uq"]]
         # [heads, dim, kv_rank] -> [heads, kv_rank, dim]: the query's unrotated part goes through W_uk^T
         self.w_uk_t = tensors[n["uk"]].view(H, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
+        self.w_uk = tensors[n["uk"]]          # as stored, for steps of whole prompts (per-head keys of the step's tokens)
         self.w_uv = tensors[n["uv"]]
         self.w_o = tensors[n["o"]]
         self.q_norm_w = tensors[n["dq_norm"]]
@@ -84,7 +86,7 @@ class LatentAttention(Mixer):
         ops.latent_attend(h, self.w_down, self.q_norm_w, self.kv_norm_w, self.eps, self.w_uq, self.w_uk_t, self.w_uv,
                           freq, ctx.batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, mixed,
                           self.num_heads, self.head_dim, self.rot_dim, self.v_head_dim, self.q_rank, self.kv_rank,
-                          self.scale, ctx.write_cache)
+                          self.scale, ctx.write_cache, w_uk=self.w_uk, shared=ctx.shared)
         if residual is None:
             out = ops.sublayer_output(T, self.hidden_size, h.device, h.dtype)
             ops.gemm(mixed, self.w_o, out)
