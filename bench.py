@@ -617,15 +617,21 @@ def run_dominex(steps: int, warmup: int, sizes=None) -> int:
                 # prompt step: causal scores and weighted sums of the latent layers (keys of KR + R, values of KR
                 # elements, H heads) and of the chunked layers (LD and LD, LH heads, blocks of CH positions)
                 pairs = lambda T, span: T * (min(T, span) + 1) / 2.0 if span >= T else T * (span + 1) / 2.0
-                attn_flops = nl * H * pairs(P, P) * 2.0 * (2 * KR + R) + nl * LH * pairs(P, CH) * 2.0 * (2 * LD)
-                grouped_flops = nl * (P * TOP * 3 * 2.0 * W * F + P * H * 2.0 * KR * (D + VD))
+                # (whole prompts: the latent layers make per-head keys of D + R and values of VD elements for the step's tokens)
+                attn_flops = nl * H * pairs(P, P) * 2.0 * (D + R + VD) + nl * LH * pairs(P, CH) * 2.0 * (2 * LD)
+                expert_flops = nl * P * TOP * 3 * 2.0 * W * F
+                head_flops = nl * P * H * 2.0 * KR * (D + VD)
                 gru_bytes = lambda T: nl * T * RW * (3 * 4 + 2)
                 fr = {}
                 k = kinds.get("prefill") or {}
                 if "attention_tile" in k:
                     fr["prefill_attention_tile_tflops"] = round(attn_flops / (k["attention_tile"][1] / 1e3) / 1e12, 2)
+                if "gemm_tc_grouped" in k:
+                    fr["prefill_experts_tcgen05_tflops"] = round(expert_flops / (k["gemm_tc_grouped"][1] / 1e3) / 1e12, 2)
+                    fr["prefill_experts_tcgen05_frac"] = round(fr["prefill_experts_tcgen05_tflops"] / peaks["bf16_tflops"], 4)
                 if "gemm_grouped" in k:
-                    fr["prefill_gemm_grouped_tflops"] = round(grouped_flops / (k["gemm_grouped"][1] / 1e3) / 1e12, 2)
+                    flops = head_flops if "gemm_tc_grouped" in k else head_flops + expert_flops
+                    fr["prefill_gemm_grouped_tflops"] = round(flops / (k["gemm_grouped"][1] / 1e3) / 1e12, 2)
                 if "min_gru" in k:
                     fr["prefill_min_gru_hbm_frac"] = round(gru_bytes(P) / (k["min_gru"][1] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
                 kd = kinds.get("decode") or {}
