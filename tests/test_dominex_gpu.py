@@ -34,9 +34,9 @@ def par(heads, kv, dim, vdim, chunk, width, scale=None, ls=1.0, rs=1.0, mlp=None
 def config(name: str) -> DominexConfig:
     if name == "a":      # sizes that take the tensor-core products; two layers that read an earlier layer's vectors
         m = DominexExperts(ff=64, experts=6, top=2)
-        layers = (lat(4, 32, 16, 32, 48, 64, mlp=m), par(4, 2, 64, 64, 24, 96, ls=0.7, rs=1.2, mlp=m),
+        layers = (lat(4, 32, 16, 32, 48, 64, mlp=m), par(8, 2, 64, 64, 24, 96, ls=0.7, rs=1.2, mlp=m),
                   lat(4, 32, 16, 32, 48, 64, kv_from=0, mlp=m), lat(4, 32, 16, 32, 48, 64, kv_from=0),
-                  par(4, 2, 64, 64, 24, 96, ls=0.7, rs=1.2, mlp=m))
+                  par(8, 2, 64, 64, 24, 96, ls=0.7, rs=1.2, mlp=m))
         return DominexConfig("Dominex", vocab_size=320, hidden_size=128, embed_scale=8.0, norm_eps=1e-5,
                              logit_softcap=20.0, layers=layers)
     if name == "b":      # odd sizes everywhere: FMA products, three query heads a key/value head, a block of 7 positions
